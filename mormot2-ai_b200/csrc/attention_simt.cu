@@ -24,7 +24,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ page_table, int max_pages, int ring_pages,
                       const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
-                      float scale, int vd, const float* __restrict__ sink) {
+                      float scale, int vd, const float* __restrict__ sink, float softcap,
+                      const T* __restrict__ gate, int gate_stride) {
   extern __shared__ __align__(16) float qs[];  // ATT_WARPS x hd
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -66,6 +67,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         for (int i = 0; i < hd; ++i) dot = fmaf(qv[i], to_f32<T>(kr[i]), dot);
       }
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);  // 0 on the first tile (m = -inf)
@@ -101,7 +103,9 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       }
     }
   }
-  const float inv = 1.0f / l;
+  // a gate per head: the head's output times the sigmoid of the token's logit for this head
+  const float inv = (gate ? 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])))
+                          : 1.0f) / l;
   T* op = out + (size_t)t * out_stride + (size_t)h * vd;
   if (VEC) {
 #pragma unroll
@@ -132,7 +136,8 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                         const int* __restrict__ page_table, int max_pages, int ring_pages,
                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                         const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
-                        float scale, int vd, const float* __restrict__ sink) {
+                        float scale, int vd, const float* __restrict__ sink, float softcap,
+                        const T* __restrict__ gate, int gate_stride) {
   extern __shared__ __align__(16) float sm[];
   const int pitch = hd + 4, pieces = hd / 4, vpitch = vd + 4, vpieces = vd / 4;
   float* qs = sm;                                  // [ATT_WARPS][hd]
@@ -181,6 +186,7 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
         dot = fmaf(qq.x, kk.x, fmaf(qq.y, kk.y, fmaf(qq.z, kk.z, fmaf(qq.w, kk.w, dot))));
       }
       s = dot * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);
@@ -204,7 +210,9 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
       }
     }
   }
-  const float inv = 1.0f / l;
+  // a gate per head: the head's output times the sigmoid of the token's logit for this head
+  const float inv = (gate ? 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])))
+                          : 1.0f) / l;
   T* op = out + (size_t)t * out_stride + (size_t)h * vd;
 #pragma unroll
   for (int d = 0; d < ATT_MAX_D / 4; ++d) {
@@ -218,13 +226,16 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 // out[t, h, :] for every token t of the step and head h. q: head h of token t at
 // q + t * q_stride + h * hd (the q part of the fused qkv rows); out: head h at
 // out + t * out_stride + h * vd. `vd`: the size of a value row (0: hd). `sink`: float32 [nh]
-// or null, one more term exp(sink[h]) in every softmax denominator of head h.
+// or null, one more term exp(sink[h]) in every softmax denominator of head h. `softcap` > 0:
+// every score s (after the scale) becomes softcap * tanh(s / softcap). `gate` (may be null):
+// head h's output of token t is multiplied by sigmoid(gate[t * gate_stride + h]).
 MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_stride,
                                 const void* kpool, const void* vpool, int dtype,
                                 const int* page_table, int max_pages, int ring_pages,
                                 const int* tok_seq, const int* tok_pos, const int* seq_slot,
                                 int T, int nh, int nkv, int hd, int window, float scale,
-                                int vd, const float* sink, void* stream) {
+                                int vd, const float* sink, float softcap, const void* gate,
+                                int gate_stride, void* stream) {
   if (T <= 0) return 0;
   if (vd <= 0) vd = hd;
   if (hd <= 0 || hd > 1024 || vd > 32 * ATT_MAX_D)
@@ -253,7 +264,7 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
     attention_shared_kernel<T_><<<grid, ATT_WARPS * 32, shared, s>>>(                         \
         (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,     \
         page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window,   \
-        scale, vd, sink);                                                                     \
+        scale, vd, sink, softcap, (const T_*)gate, gate_stride);                                                               \
   }
     if (dtype == MB_F32) GOS(float) else GOS(__nv_bfloat16)
 #undef GOS
@@ -263,7 +274,7 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
   attention_simt_kernel<T_, V_><<<grid, ATT_WARPS * 32, smem, s>>>(                           \
       (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,       \
       page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale, \
-      vd, sink)
+      vd, sink, softcap, (const T_*)gate, gate_stride)
   if (dtype == MB_F32) {
     if (vec) GO(float, true); else GO(float, false);
   } else {

@@ -447,3 +447,160 @@ MB_EXPORT int mb_scale(float* x, long long total, float factor, void* stream) {
   mb_launch(scale_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)total, factor);
   MB_CHECK_LAUNCH("mb_scale");
 }
+
+// ------------------------------------------------------------------ a normed sublayer output
+// x[t] += w * (y[t] / rms(y[t])) for a sublayer whose output is normed before it joins the
+// residual; y is a float32 tensor [T, H] or the sum of `parts` split sums [parts][T][H] of the
+// product before (added in split order). `h` (may be null): the new residual row rounded to
+// the activation type, which the next sublayer reads. One block per row; sums in float32.
+template <typename TW, typename TO>
+__global__ void norm_add_kernel(const float* __restrict__ y, int parts, size_t part_stride,
+                                const TW* __restrict__ w, float eps, float* __restrict__ x,
+                                TO* __restrict__ h, int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  __shared__ float red[33];
+  extern __shared__ float rowbuf[];  // H floats
+  const int r = blockIdx.x;
+  const float* yr = y + (size_t)r * H;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float v = parts > 1 ? sum_parts(yr + c, parts, part_stride) : yr[c];
+    rowbuf[c] = v;
+    sum = fmaf(v, v, sum);
+  }
+  sum = block_sum(sum, red);
+  const float inv = 1.0f / sqrtf(sum / (float)H + eps);
+  float* xr = x + (size_t)r * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    const float n = rowbuf[c] * inv;
+    const float v = xr[c] + to_f32<TW>(w[c]) * n;
+    xr[c] = v;
+    if (h) h[(size_t)r * H + c] = from_f32<TO>(v);
+  }
+}
+
+MB_EXPORT int mb_norm_add(const float* y, int parts, long long part_stride, const void* w,
+                          int w_dtype, float eps, float* x, void* h, int h_dtype, int T, int H,
+                          void* stream) {
+  if (T <= 0) return 0;
+  if (parts < 1) MB_FAIL("mb_norm_add: %d parts", parts);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = H >= 2048 ? 512 : H >= 512 ? 256 : 128;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) MB_FAIL("mb_norm_add: rows of %d values", H);
+#define GO(TW_, TO_)                                                                         \
+  {                                                                                          \
+    static size_t configured = 48 * 1024;                                                    \
+    if (smem > configured) {                                                                 \
+      cudaFuncSetAttribute(norm_add_kernel<TW_, TO_>,                                        \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);         \
+      configured = 200 * 1024;                                                               \
+    }                                                                                        \
+    mb_launch(norm_add_kernel<TW_, TO_>, dim3(T), dim3(threads), smem, s, y, parts,          \
+              (size_t)part_stride, (const TW_*)w, eps, x, (TO_*)h, H);                       \
+  }
+  if (w_dtype == MB_F32) {
+    if (h_dtype == MB_F32) GO(float, float) else GO(float, __nv_bfloat16)
+  } else {
+    if (h_dtype == MB_F32) GO(__nv_bfloat16, float) else GO(__nv_bfloat16, __nv_bfloat16)
+  }
+#undef GO
+  MB_CHECK_LAUNCH("mb_norm_add");
+}
+
+// ------------------------------------------------------------------ the residual as an operand
+// h = x rounded to the activation type (a sublayer that reads the residual itself).
+template <typename TO>
+__global__ void cast_rows_kernel(const float* __restrict__ x, TO* __restrict__ h, size_t total) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x)
+    h[i] = from_f32<TO>(x[i]);
+}
+
+MB_EXPORT int mb_cast_rows(const float* x, void* h, int h_dtype, long long total, void* stream) {
+  if (total <= 0) return 0;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  if (h_dtype == MB_F32)
+    mb_launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x,
+              (float*)h, (size_t)total);
+  else
+    mb_launch(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+              x, (__nv_bfloat16*)h, (size_t)total);
+  MB_CHECK_LAUNCH("mb_cast_rows");
+}
+
+// ------------------------------------------------------------------ an activation of one input
+// out[t, c] = act(in[t, c]) (* table[ids[t], col0 + c] when a table is given: a factor that
+// the token itself brings), act = SiLU (0), the tanh form of GELU (1) or relu(z)^2 (3).
+enum { ACT_RELU_SQUARED = 3 };
+template <typename T, typename TW>
+__global__ void unary_act_kernel(const T* __restrict__ in, int ld_in, T* __restrict__ out, int N,
+                                 int act, const TW* __restrict__ table, int ld_table, int col0,
+                                 const int* __restrict__ ids, int V) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int t = blockIdx.y;
+  const T* row = in + (size_t)t * ld_in;
+  const TW* trow = nullptr;
+  if (table) {
+    int id = ids[t];
+    if (id < 0 || id >= V) id = 0;  // the host refuses such ids before the step
+    trow = table + (size_t)id * ld_table + col0;
+  }
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < N; c += gridDim.x * blockDim.x) {
+    const float z = to_f32<T>(row[c]);
+    float a;
+    if (act == ACT_RELU_SQUARED) {
+      const float p = fmaxf(z, 0.f);
+      a = p * p;
+    } else {
+      a = act_of(z, act);
+    }
+    if (trow) a *= to_f32<TW>(trow[c]);
+    out[(size_t)t * N + c] = from_f32<T>(a);
+  }
+}
+
+MB_EXPORT int mb_unary_act(const void* in, int ld_in, void* out, int dtype, int T, int N, int act,
+                           const void* table, int table_dtype, int ld_table, int col0,
+                           const int* ids, int V, void* stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (act != ACT_SILU && act != ACT_GELU_TANH && act != ACT_RELU_SQUARED)
+    MB_FAIL("mb_unary_act: activation %d", act);
+  if (table != nullptr && ids == nullptr) MB_FAIL("mb_unary_act: a table without token ids");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = N >= 256 ? 256 : 64;
+  dim3 grid(max(1, min((N + threads - 1) / threads, 64)), T);
+#define GO(T_, TW_)                                                                           \
+  mb_launch(unary_act_kernel<T_, TW_>, grid, dim3(threads), 0, s, (const T_*)in, ld_in,        \
+            (T_*)out, N, act, (const TW_*)table, ld_table, col0, ids, V)
+  if (dtype == MB_F32) {
+    if (table_dtype == MB_F32) GO(float, float); else GO(float, __nv_bfloat16);
+  } else {
+    if (table_dtype == MB_F32) GO(__nv_bfloat16, float); else GO(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef GO
+  MB_CHECK_LAUNCH("mb_unary_act");
+}
+
+// ------------------------------------------------------------------ a soft cap
+// x = cap * tanh(x / cap), float32 in place (logits).
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
+MB_EXPORT int mb_softcap(float* x, long long total, float cap, void* stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.f)) MB_FAIL("mb_softcap: a cap of %g", (double)cap);
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  mb_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)total,
+            cap);
+  MB_CHECK_LAUNCH("mb_softcap");
+}

@@ -13,6 +13,8 @@
 //   mlstm_scan    log gates i = cap tanh((zi + bi)/cap), f = logsigmoid(cap tanh((zf + bf)/cap));
 //                 m' = max(f + m, i); S <- e^(f+m-m') S + e^(i-m') k v^T; n likewise with k;
 //                 o = S^T q / (max(|n.q|, e^(-m')) + 1e-6); then o / rms(o) * norm * sigmoid(g)
+//   retention_scan  q, k turned by the position; S <- decay S + (k / sqrt(D)) v^T; o = S^T q;
+//                 then o / rms(o) * silu(g)
 #include "common.cuh"
 
 MB_DEFINE_LAST_ERROR
@@ -220,7 +222,8 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k,
       st[cc] = to_f32<T>(h[(size_t)(t0 + n - 1) * W + cc]);
 }
 
-// out[t, hd, :] = o / rms(o) * normw * gate(g) for every token and head, a warp each; o: raw
+// out[t, hd, :] = o / rms(o) * normw * gate(g) for every token and head, a warp each (normw
+// null: ones); o: raw
 // [T, H * DV] float32; g: the gates' logits, head hd of token t at g + t * ldg + hd * DV;
 // gate 0: g sigmoid(g), 1: sigmoid(g).
 template <typename T>
@@ -239,7 +242,8 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ raw, const float
   const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)DV + eps);
   for (int i = lane; i < DV; i += 32) {
     const float gi = gg[i], sig = 1.0f / (1.0f + expf(-gi));
-    out[(size_t)idx * DV + i] = from_f32<T>(o[i] * inv * normw[hd * DV + i] * (gate ? sig : gi * sig));
+    const float w = normw ? normw[hd * DV + i] : 1.0f;
+    out[(size_t)idx * DV + i] = from_f32<T>(o[i] * inv * w * (gate ? sig : gi * sig));
   }
 }
 
@@ -587,6 +591,221 @@ MB_EXPORT int mb_mlstm_scan(const float* z, int ld, int cq, int ck, int cv, int 
 #undef GOR
 #undef GO
   MB_CHECK_LAUNCH("mb_mlstm_scan");
+}
+
+// ------------------------------------------------------------------ retention
+// Linear attention with a constant decay per head and no denominator. z: float32 [T, ld], the
+// fused projection: q at column cq + hd * D, k at ck + hd * D, v at cv + hd * DV, the output
+// gate's logit at cg + hd * DV. q and k turn by the token's position in the rotate-half pairing
+// over their first rot_dim values (angle = f32(inv_freq[i] * pos)); k is then multiplied by
+// k_scale. S <- decay[hd] S + k v^T; o = S^T q (the state after the token); then
+// o / rms(o) * silu(g). State of a slot, per head: D x DV. out / raw as in wkv_scan_kernel.
+template <typename T, int R>
+__global__ void __launch_bounds__(512, 1)
+retention_scan_kernel(const float* __restrict__ z, int ld, int cq, int ck, int cv, int cg,
+                      const float* __restrict__ decay, float k_scale,
+                      const float* __restrict__ inv_freq, int rot_dim,
+                      const int* __restrict__ tok_pos, float eps, float* __restrict__ state,
+                      size_t state_stride, size_t state_off, const int* __restrict__ seq_start,
+                      const int* __restrict__ seq_slot, T* __restrict__ out,
+                      float* __restrict__ raw, int H, int D, int DV) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  extern __shared__ __align__(16) float rt_smem[];
+  const int NS = gridDim.z, CW = (DV + NS - 1) / NS;
+  const int c0 = blockIdx.z * CW, cw = max(0, min(DV, c0 + CW) - c0);
+  const int Cp = pad32(CW), P = blockDim.x / Cp;
+  const int part = threadIdx.x / Cp, j = threadIdx.x - part * Cp;
+  const int per = (D + P - 1) / P, i0 = min(D, part * per), cnt = min(D, i0 + per) - i0;
+  float* S = rt_smem;                                   // [D][CW] (R = 0 only)
+  float2* qk = (float2*)(S + (R > 0 ? 0 : ((D * CW + 3) & ~3)));   // [CT][D]: q, k (turned, scaled)
+  float* sv = (float*)(qk + SCAN_CT * D + 64);          // [CT][CW] v (64 entries of room behind qk)
+  float* sg = sv + SCAN_CT * CW;                        // [CT][CW] the output gate's logit
+  float* snum = sg + SCAN_CT * CW;                      // [CT][P][CW] S^T q, summed over a part's rows
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int t0 = seq_start[b], n = seq_start[b + 1] - t0;
+  float* Sg = state + (size_t)seq_slot[b] * state_stride + state_off +
+              (size_t)hd * D * DV + c0;                 // row i of this slice at Sg + i * DV
+  const bool own = j < cw && part < P;
+  const float a = decay[hd];
+  const int half = rot_dim >> 1;
+  float Sr[R > 0 ? R : 1];
+  if (R > 0) {
+#pragma unroll
+    for (int q = 0; q < (R > 0 ? R : 1); ++q)
+      Sr[q] = (own && q < cnt) ? Sg[(size_t)(i0 + q) * DV + j] : 0.f;
+  } else {
+    for (int e = threadIdx.x; e < D * cw; e += blockDim.x) {
+      const int i = e / cw, jj = e - i * cw;
+      S[i * CW + jj] = Sg[(size_t)i * DV + jj];
+    }
+  }
+  for (int c = 0; c < n; c += SCAN_CT) {
+    const int cn = min(SCAN_CT, n - c);
+    for (int e = threadIdx.x; e < cn * D; e += blockDim.x) {
+      const int tt = e / D, i = e - tt * D;
+      const float* zr = z + (size_t)(t0 + c + tt) * ld;
+      float qv = zr[cq + hd * D + i], kv = zr[ck + hd * D + i];
+      if (i < rot_dim) {
+        const bool lo = i < half;
+        const int f = lo ? i : i - half, other = lo ? i + half : i - half;
+        const float angle = inv_freq[f] * (float)tok_pos[t0 + c + tt];   // float32 product
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const float qo = zr[cq + hd * D + other], ko = zr[ck + hd * D + other];
+        qv = lo ? qv * cs - qo * sn : qv * cs + qo * sn;
+        kv = lo ? kv * cs - ko * sn : kv * cs + ko * sn;
+      }
+      qk[e] = make_float2(qv, kv * k_scale);
+    }
+    for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
+      const int tt = e / cw, jj = e - tt * cw;
+      const float* zr = z + (size_t)(t0 + c + tt) * ld;
+      sv[tt * CW + jj] = zr[cv + hd * DV + c0 + jj];
+      sg[tt * CW + jj] = zr[cg + hd * DV + c0 + jj];
+    }
+    __syncthreads();
+    if (own) {
+      for (int tt = 0; tt < cn; ++tt) {
+        const float vj = sv[tt * CW + j];
+        const float2* x = qk + tt * D;
+        float num = 0.f;
+        if (R > 0) {
+          float n4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int q = 0; q < (R > 0 ? R : 1); ++q) {
+            const float2 xi = x[i0 + q];      // no branch, as in wkv_scan_kernel
+            const float s = fmaf(a, Sr[q], xi.y * vj);
+            Sr[q] = s;
+            const float with = fmaf(s, xi.x, n4[q & 3]);
+            n4[q & 3] = q < cnt ? with : n4[q & 3];
+          }
+          num = (n4[0] + n4[1]) + (n4[2] + n4[3]);
+        } else {
+          for (int ib = i0; ib < i0 + cnt; ib += 8) {   // eight rows at a time, as in wkv_scan_kernel
+            float2 xi[8];
+            float sc[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const int i = min(ib + q, i0 + cnt - 1);
+              xi[q] = x[i];
+              sc[q] = S[i * CW + j];
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (ib + q < i0 + cnt) {
+                const float s = fmaf(a, sc[q], xi[q].y * vj);
+                S[(ib + q) * CW + j] = s;
+                num = fmaf(s, xi[q].x, num);
+              }
+            }
+          }
+        }
+        snum[(tt * P + part) * CW + j] = num;
+      }
+    }
+    __syncthreads();
+    if (raw != nullptr) {
+      for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
+        const int tt = e / cw, jj = e - tt * cw;
+        float num = 0.f;
+        for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * CW + jj];
+        raw[(size_t)(t0 + c + tt) * H * DV + hd * DV + c0 + jj] = num;
+      }
+    } else {
+      // one slice: the head's unit norm and the gate here, a warp a token
+      for (int tt = warp; tt < cn; tt += warps) {
+        float nv[8];   // value rows of up to 256 a lane's eight; beyond, the sums are formed again
+        float ss = 0.f;
+        for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+          float num = 0.f;
+          for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * CW + i];
+          if (q < 8) nv[q] = num;
+          ss = fmaf(num, num, ss);
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)DV + eps);
+        T* orow = out + (size_t)(t0 + c + tt) * H * DV + hd * DV;
+        for (int i = lane, q = 0; i < DV; i += 32, ++q) {
+          float num = 0.f;
+          if (q < 8) {
+            num = nv[q];
+          } else {
+            for (int pp = 0; pp < P; ++pp) num += snum[(tt * P + pp) * CW + i];
+          }
+          const float gi = sg[tt * CW + i];
+          orow[i] = from_f32<T>(num * inv * (gi / (1.0f + expf(-gi))));
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (R > 0) {
+#pragma unroll
+    for (int q = 0; q < (R > 0 ? R : 1); ++q)
+      if (own && q < cnt) Sg[(size_t)(i0 + q) * DV + j] = Sr[q];
+  } else {
+    for (int e = threadIdx.x; e < D * cw; e += blockDim.x) {
+      const int i = e / cw, jj = e - i * cw;
+      Sg[(size_t)i * DV + jj] = S[i * CW + jj];
+    }
+  }
+}
+
+static size_t retention_smem_bytes(int D, int CW, int P, int R) {
+  const size_t state = R ? 0 : (size_t)((D * CW + 3) & ~3);
+  return (state + (size_t)SCAN_CT * (2 * D + (2 + P) * CW) + 64 * 2) * sizeof(float);
+}
+
+// `decay`: float32 [H] on the device. `inv_freq`: float32 [rot_dim / 2] (may be null when
+// rot_dim is 0). `raw`: float32 [T, H * DV] of scratch, as in mb_wkv_scan.
+MB_EXPORT int mb_retention_scan(const float* z, int ld, int cq, int ck, int cv, int cg,
+                                const float* decay, float k_scale, const float* inv_freq,
+                                int rot_dim, const int* tok_pos, float eps, float* state,
+                                long long state_stride, long long state_off,
+                                const int* seq_start, const int* seq_slot, void* out, float* raw,
+                                int dtype, int T_, int B, int H, int D, int DV, void* stream) {
+  if (B <= 0) return 0;
+  if (D <= 0 || DV <= 0 || D > 512 || DV > 512)
+    MB_FAIL("mb_retention_scan: heads of %d x %d values (at most 512 each)", D, DV);
+  if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || (rot_dim > 0 && inv_freq == nullptr))
+    MB_FAIL("mb_retention_scan: %d of %d values rotate", rot_dim, D);
+  const int NS = raw ? scan_slices(B, H, D, DV, 32) : 1;
+  const int CW = (DV + NS - 1) / NS;
+  const int P = scan_parts(CW), per = (D + P - 1) / P;
+  const int R = per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : 0;
+  const size_t smem = retention_smem_bytes(D, CW, P, R);
+  if (smem > 200 * 1024)
+    MB_FAIL("mb_retention_scan: heads of %d x %d values (what a block stages must fit 200 KB)",
+            D, DV);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = (CW + 31) / 32 * 32 * P;
+  float* raw_used = NS > 1 ? raw : nullptr;
+#define GO(T_t, R_)                                                                            \
+  {                                                                                            \
+    static size_t configured = 48 * 1024;                                                      \
+    if (smem > configured) {                                                                   \
+      cudaFuncSetAttribute(retention_scan_kernel<T_t, R_>,                                     \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
+      configured = 200 * 1024;                                                                 \
+    }                                                                                          \
+    mb_launch(retention_scan_kernel<T_t, R_>, dim3(B, H, NS), dim3(threads), smem, s, z, ld,   \
+              cq, ck, cv, cg, decay, k_scale, inv_freq, rot_dim, tok_pos, eps, state,          \
+              (size_t)state_stride, (size_t)state_off, seq_start, seq_slot, (T_t*)out,         \
+              raw_used, H, D, DV);                                                             \
+    if (NS > 1) launch_head_norm<T_t>(raw, z + cg, ld, nullptr, eps, 0, out, T_, H, DV, s);    \
+  }
+#define GOR(T_t)                                                                               \
+  switch (R) {                                                                                 \
+    case 8: GO(T_t, 8) break;                                                                  \
+    case 16: GO(T_t, 16) break;                                                                \
+    case 32: GO(T_t, 32) break;                                                                \
+    default: GO(T_t, 0)                                                                        \
+  }
+  if (dtype == MB_F32) GOR(float) else GOR(__nv_bfloat16)
+#undef GOR
+#undef GO
+  MB_CHECK_LAUNCH("mb_retention_scan");
 }
 
 // ------------------------------------------------------------------ tanh between two products

@@ -18,7 +18,9 @@ __device__ __forceinline__ float norm_w(const void* w, int w_bf16, int i) {
 // token. One warp per
 // (token, head): RMSNorm over the head with q_norm / k_norm (null: no norm), rotate_half over
 // the first rot_dim values with angle = f32(inv_freq[i] * pos), q written back in place, k and
-// v (when write_kv) stored in the cache at the token's slot and position.
+// v (when write_kv) stored in the cache at the token's slot and position. `ld`: the row pitch
+// of qkv (columns behind the heads belong to someone else). `unit_after`: instead of a weighted
+// norm before the rotation, q and k are divided by their root mean square after it.
 #define QK_WARPS 4
 template <typename T, typename TW>
 __global__ void qk_norm_rope_store_kernel(
@@ -26,7 +28,8 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos,
     const int* __restrict__ page_table, int max_pages, int ring_pages, T* __restrict__ kpool,
-    T* __restrict__ vpool, int nh, int nkv, int hd, int write_kv, int vd) {
+    T* __restrict__ vpool, int nh, int nkv, int hd, int write_kv, int vd, int ld,
+    int unit_after) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ float heads[];  // QK_WARPS x hd
@@ -37,8 +40,7 @@ __global__ void qk_norm_rope_store_kernel(
   if (head >= total) return;
   const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
   if (!is_q && !write_kv) return;
-  const size_t width = (size_t)(nh + nkv) * hd + (size_t)nkv * vd;
-  T* src = qkv + (size_t)t * width +
+  T* src = qkv + (size_t)t * ld +
            (head < nh + nkv ? (size_t)head * hd
                             : (size_t)(nh + nkv) * hd + (size_t)(head - nh - nkv) * vd);
   float* buf = heads + warp * hd;
@@ -62,12 +64,13 @@ __global__ void qk_norm_rope_store_kernel(
     sum = fmaf(v, v, sum);
   }
   sum = warp_sum(sum);
-  if (w) {
+  if (w && !unit_after) {
     const float inv = 1.0f / sqrtf(sum / (float)hd + eps);
     for (int i = lane; i < hd; i += 32) buf[i] = to_f32<TW>(w[i]) * (buf[i] * inv);
   }
   __syncwarp();
   const int half = rot_dim >> 1;
+  float after = 0.f;   // the sum of squares of the head as it is after the rotation
   for (int i = lane; i < hd; i += 32) {
     float v = buf[i];
     if (i < rot_dim) {
@@ -76,7 +79,22 @@ __global__ void qk_norm_rope_store_kernel(
       const float c = cosf(angle), s = sinf(angle);
       v = i < half ? buf[i] * c - buf[i + half] * s : buf[i] * c + buf[i - half] * s;
     }
-    dst[i] = from_f32<T>(v);
+    if (unit_after) after = fmaf(v, v, after);
+    else dst[i] = from_f32<T>(v);
+  }
+  if (!unit_after) return;
+  // the head over its root mean square, formed after the rotation, without a weight: the
+  // rotated values are formed once more (buf still holds the unrotated head)
+  const float inv = 1.0f / sqrtf(warp_sum(after) / (float)hd + eps);
+  for (int i = lane; i < hd; i += 32) {
+    float v = buf[i];
+    if (i < rot_dim) {
+      const int f = i < half ? i : i - half;
+      const float angle = inv_freq[f] * (float)pos;
+      const float c = cosf(angle), s = sinf(angle);
+      v = i < half ? buf[i] * c - buf[i + half] * s : buf[i] * c + buf[i - half] * s;
+    }
+    dst[i] = from_f32<T>(v * inv);
   }
 }
 
@@ -97,7 +115,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
                const int* __restrict__ tok_pos,
                const int* __restrict__ page_table, int max_pages, int ring_pages,
                __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
-               int nkv, int write_kv) {
+               int nkv, int write_kv, int ld, int unit_after) {
   MB_TRACE_BEGIN();
   constexpr int HD = 64 * V, HALF = 32 * V;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -118,7 +136,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
   if (live) {
     const int pos = tok_pos[t];
     if (is_q) {
-      dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
+      dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * ld + col;
     } else {
       const int g = is_k ? head - nh : head - nh - nkv;
       const size_t row = kv_row(page_table, max_pages, ring_pages, tok_slot[t], pos, nkv, g);
@@ -126,7 +144,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
     }
     if (is_q || is_k) {
       const void* w = is_q ? q_norm : k_norm;
-      normed = w != nullptr;
+      normed = w != nullptr && !unit_after;
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         wa[j] = normed ? norm_w(w, w_bf16, V * lane + j) : 1.f;
@@ -141,7 +159,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
   if (!live) return;
   float a[V], b[V];
   if (PARTIAL) {
-    const float* src0 = partial + (size_t)t * total * HD + col;
+    const float* src0 = partial + (size_t)t * ld + col;
     // up to eight parts asked for at once, then added in split order
 #pragma unroll
     for (int j = 0; j < V; ++j) a[j] = b[j] = 0.f;
@@ -165,7 +183,7 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
         }
     }
   } else {
-    const __nv_bfloat16* src = qkv + (size_t)t * total * HD + col;
+    const __nv_bfloat16* src = qkv + (size_t)t * ld + col;
 #pragma unroll
     for (int j = 0; j < V; ++j) {
       a[j] = __bfloat162float(src[j]);
@@ -190,6 +208,18 @@ qk_narrow_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ part
       const float ra = a[j] * cs[j] - b[j] * sn[j], rb = b[j] * cs[j] + a[j] * sn[j];
       a[j] = ra;
       b[j] = rb;
+    }
+    if (unit_after) {   // over the root mean square of the rotated head, no weight
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < V; ++j) sum = fmaf(a[j], a[j], fmaf(b[j], b[j], sum));
+      sum = warp_sum(sum);
+      const float inv = 1.0f / sqrtf(sum / (float)HD + eps);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        a[j] *= inv;
+        b[j] *= inv;
+      }
     }
   }
 #pragma unroll
@@ -235,7 +265,7 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
                const int* __restrict__ tok_pos,
                const int* __restrict__ page_table, int max_pages, int ring_pages,
                __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, int nh,
-               int nkv, int write_kv, int passes) {
+               int nkv, int write_kv, int passes, int ld, int unit_after) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int HALF = HD / 2, L = HALF / 8, HPP = 32 / L;  // lanes a head, heads a pass
@@ -257,7 +287,7 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
       const int head = (group0 + i) * HPP + hl;
       raw[i][0] = raw[i][1] = make_uint4(0u, 0u, 0u, 0u);
       if (i < passes && head < total && (head < nh || write_kv)) {
-        const __nv_bfloat16* src = qkv + (size_t)t * total * HD + (size_t)head * HD + 8 * sl;
+        const __nv_bfloat16* src = qkv + (size_t)t * ld + (size_t)head * HD + 8 * sl;
         raw[i][0] = *reinterpret_cast<const uint4*>(src);
         raw[i][1] = *reinterpret_cast<const uint4*>(src + HALF);
       }
@@ -277,7 +307,7 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
     for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.f;
     if (live) {
       if (PARTIAL) {
-        const float* src0 = partial + (size_t)t * total * HD + col;
+        const float* src0 = partial + (size_t)t * ld + col;
 #pragma unroll 2
         for (int p = 0; p < parts; ++p) {
           const float4* sa = reinterpret_cast<const float4*>(src0 + (size_t)p * part_stride);
@@ -318,7 +348,7 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
       }
       if (live && (is_q || is_k)) {
         const void* w = is_q ? q_norm : k_norm;
-        if (w) {
+        if (w && !unit_after) {
           const float inv = 1.0f / sqrtf(sum / (float)HD + eps);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -333,11 +363,26 @@ qk_wide_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ partia
           b[j] = rb;
         }
       }
+      if (unit_after) {   // over the root mean square of the rotated head, no weight
+        float after = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) after = fmaf(a[j], a[j], fmaf(b[j], b[j], after));
+#pragma unroll
+        for (int o = L / 2; o > 0; o >>= 1) after += __shfl_xor_sync(0xffffffffu, after, o);
+        if (live && (is_q || is_k)) {
+          const float inv = 1.0f / sqrtf(after / (float)HD + eps);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            a[j] *= inv;
+            b[j] *= inv;
+          }
+        }
+      }
     }
     if (!live) continue;
     __nv_bfloat16* dst;
     if (is_q) {
-      dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * total * HD + col;
+      dst = q_out ? q_out + (size_t)t * nh * HD + col : qkv + (size_t)t * ld + col;
     } else {
       const int g = is_k ? head - nh : head - nh - nkv;
       const size_t row =
@@ -359,9 +404,13 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
                                     const int* tok_slot, const int* tok_pos,
                                     const int* page_table, int max_pages, int ring_pages,
                                     void* kpool, void* vpool, int T, int nh, int nkv, int hd,
-                                    int write_kv, int vd, void* stream) {
+                                    int write_kv, int vd, int ld, int unit_after,
+                                    void* stream) {
   if (T <= 0) return 0;
   if (vd <= 0) vd = hd;
+  const int width = (nh + nkv) * hd + nkv * vd;
+  if (ld <= 0) ld = width;
+  if (ld < width) MB_FAIL("mb_qk_norm_rope_store: a row pitch of %d for %d values", ld, width);
   if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1))
     MB_FAIL("mb_qk_norm_rope_store: %d of %d values rotate", rot_dim, hd);
   if (hd <= 0 || hd > 1024) MB_FAIL("mb_qk_norm_rope_store: heads of %d", hd);
@@ -370,7 +419,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   const bool aligned = !(((uintptr_t)qkv | (uintptr_t)partial | (uintptr_t)q_out |
                           (uintptr_t)kpool | (uintptr_t)vpool) & 15) && (part_stride & 3) == 0;
   const bool fast = dtype == MB_BF16 && rot_dim == hd && (hd == 64 || hd == 128 || hd == 256) &&
-                    aligned && vd == hd;
+                    aligned && vd == hd && ld % 8 == 0;
   if ((partial || q_out) && !fast)
     MB_FAIL("mb_qk_norm_rope_store: partial sums or a separate q for heads of %d values "
             "(%d rotate)%s are not supported", hd, rot_dim, aligned ? "" : ", not 16-byte aligned,");
@@ -382,7 +431,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   mb_launch(qk_narrow_kernel<V_, P_>, grid, dim3(QK_WARPS * 32), 0, s, (bf*)qkv, partial,      \
       parts, (size_t)part_stride, (bf*)q_out, q_norm, k_norm, w_bf16, eps, inv_freq, tok_slot, \
       tok_pos, page_table, max_pages, ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv,   \
-      write_kv)
+      write_kv, ld, unit_after)
 #define QKN_V(P_)                                                                              \
   if (hd == 64) QKN(1, P_); else if (hd == 128) QKN(2, P_); else QKN(4, P_)
       if (partial) { QKN_V(true); } else { QKN_V(false); }
@@ -398,7 +447,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   mb_launch(qk_wide_kernel<HD_, P_>, fgrid, dim3(warps * 32), 0, s, (bf*)qkv, partial, parts,  \
       (size_t)part_stride, (bf*)q_out, q_norm, k_norm, w_bf16, eps, inv_freq, tok_slot,        \
       tok_pos, page_table, max_pages, ring_pages, (bf*)kpool, (bf*)vpool, nh, nkv,   \
-      write_kv, passes)
+      write_kv, passes, ld, unit_after)
 #define QKF_V(P_)                                                                              \
   if (hd == 64) QKF(64, P_); else if (hd == 128) QKF(128, P_); else QKF(256, P_)
     if (partial) { QKF_V(true); } else { QKF_V(false); }
@@ -411,7 +460,7 @@ MB_EXPORT int mb_qk_norm_rope_store(void* qkv, const float* partial, int parts,
   mb_launch(qk_norm_rope_store_kernel<T_, TW_>, dim3(grid), dim3(QK_WARPS * 32), smem, s,                         \
       (T_*)qkv, (const TW_*)q_norm, (const TW_*)k_norm, eps, inv_freq, rot_dim, tok_slot,      \
       tok_pos, page_table, max_pages, ring_pages, (T_*)kpool, (T_*)vpool, nh, nkv,   \
-      hd, write_kv, vd)
+      hd, write_kv, vd, ld, unit_after)
   if (dtype == MB_F32 && w_dtype == MB_F32) QK_LAUNCH(float, float);
   else if (dtype == MB_F32) QK_LAUNCH(float, __nv_bfloat16);
   else if (w_dtype == MB_F32) QK_LAUNCH(__nv_bfloat16, float);

@@ -158,12 +158,15 @@ class Runtime:
         K.latent_attention(q, out, step, line, nh, kv_rank, rot_dim, window, scale)
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd=0,
-                  sink=None) -> None:
+                  sink=None, softcap=0.0, gate=None, gate_stride=0) -> None:
         """``vd``: the size of a value row where it differs from ``hd``; ``sink``: float32
-        [nh], one more term of every softmax denominator."""
-        if self.fast_kernels and (not vd or vd == hd):
+        [nh], one more term of every softmax denominator; ``softcap`` > 0: a cap
+        c tanh(s / c) on the scaled scores; ``gate``: one logit per (token, head) whose sigmoid
+        multiplies the head's output."""
+        if self.fast_kernels and (not vd or vd == hd) and not softcap and gate is None:
             from ..parts import attention_fast
             if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale,
                                   sink):
                 return
-        K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink)
+        K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink,
+                         softcap, gate, gate_stride)

@@ -75,7 +75,9 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_moe_route": "routing", "mb_moe_plan": "routing", "mb_moe_route_plan": "routing", "mb_moe_gemm": "products",
             "mb_moe_combine": "routing", "mb_stream_step": "norms", "mb_add_scaled": "norms",
             "mb_token_shift": "recurrence", "mb_wkv_scan": "recurrence",
-            "mb_mlstm_scan": "recurrence", "mb_tanh": "recurrence"}
+            "mb_mlstm_scan": "recurrence", "mb_tanh": "recurrence",
+            "mb_retention_scan": "recurrence", "mb_norm_add": "norms", "mb_cast_rows": "norms",
+            "mb_unary_act": "activation", "mb_softcap": "activation"}
 
 
 class Timing:
@@ -222,10 +224,14 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 
 def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, nh, nkv, hd,
                        write_kv: bool, partial: Optional[torch.Tensor] = None,
-                       q_out: Optional[torch.Tensor] = None, vd: int = 0) -> None:
+                       q_out: Optional[torch.Tensor] = None, vd: int = 0,
+                       unit_after: bool = False) -> None:
     """Per-head norm of q and k, rotary positions, q in place (or into ``q_out``), k and v into
     the cache line. ``partial`` [parts, T, width] float32: the split sums of the q/k/v product,
-    which stand for ``qkv`` (then None) and are added up here."""
+    which stand for ``qkv`` (then None) and are added up here. A row may hold more columns
+    behind q, k and v (another projection of the same product); they are left alone.
+    ``unit_after``: q and k are divided by their root mean square after the rotation, without
+    a weight, instead of the weighted norm before it."""
     if partial is not None:
         assert partial.dtype == torch.float32 and partial.is_contiguous() and q_out is not None
         T, width = partial.shape[1], partial.shape[2]
@@ -235,7 +241,7 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
         _contig(qkv, "qkv")
         dtype_code = code_of(qkv.dtype)
     vd = vd or hd
-    assert width == (nh + nkv) * hd + nkv * vd
+    assert width >= (nh + nkv) * hd + nkv * vd
     if rot_dim > 0 and inv_freq is None:
         raise KernelError("a rotary encoding without its frequencies (is the position "
                           "encoding bound?)")
@@ -246,18 +252,21 @@ def qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim, step, line, 
     wd = code_of(q_norm.dtype) if q_norm is not None else F32
     _call("rope", "mb_qk_norm_rope_store",
           [_vp, _vp, _i, _ll, _vp, _i, _vp, _vp, _i, _f, _vp, _i, _vp, _vp, _vp, _i, _i,
-           _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+           _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
           _ptr(qkv), _ptr(partial), partial.shape[0] if partial is not None else 0,
           partial.stride(0) if partial is not None else 0, _ptr(q_out), dtype_code,
           _ptr(q_norm), _ptr(k_norm), wd, float(eps),
           _ptr(inv_freq), rot_dim, _ptr(step.tok_slot), _ptr(step.tok_pos),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(line.k), _ptr(line.v),
-          T, nh, nkv, hd, 1 if write_kv else 0, vd, _stream())
+          T, nh, nkv, hd, 1 if write_kv else 0, vd, width, 1 if unit_after else 0, _stream())
 
 
 # "clamped_swish": g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
-ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED_SWISH = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_CLAMPED_SWISH, ACT_RELU_SQUARED = 0, 1, 2, 3
 ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "clamped_swish": ACT_CLAMPED_SWISH}
+# activations of one input (a feed-forward without a gate): act(W_up h)
+UNARY_ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH,
+                     "relu_squared": ACT_RELU_SQUARED}
 
 
 def dynamic_tanh(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: torch.Tensor,
@@ -311,6 +320,58 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int,
           _ptr(gate_up), _ptr(out), code_of(out.dtype), T, I, act, _ptr(gate_bias),
           _ptr(up_bias), code_of(biases[0].dtype) if biases else F32, _ptr(x), _ptr(x_bias),
           x.shape[1] if x is not None else 0, float(limit), _stream())
+
+
+def norm_add(y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tensor,
+             h: Optional[torch.Tensor] = None) -> None:
+    """x += w * y / rms(y), row by row (float32); ``y`` [T, H] float32 or the split sums
+    [parts, T, H] of a product, added up here in split order. ``h`` [T, H] (activation type):
+    receives the new x rounded, for the sublayer that reads the residual next."""
+    T, H = x.shape
+    assert x.dtype == torch.float32 and y.dtype == torch.float32 and w.numel() == H
+    _contig(x, "x"), _contig(y, "y")
+    parts, stride = (1, 0) if y.dim() == 2 else (y.shape[0], y.stride(0))
+    assert y.shape[-2:] == (T, H)
+    if h is not None:
+        assert h.shape == (T, H) and h.is_contiguous()
+    _call("elementwise", "mb_norm_add", [_vp, _i, _ll, _vp, _i, _f, _vp, _vp, _i, _i, _i, _vp],
+          _ptr(y), parts, stride, _ptr(w), code_of(w.dtype), float(eps), _ptr(x), _ptr(h),
+          code_of(h.dtype) if h is not None else F32, T, H, _stream())
+
+
+def cast_rows(x: torch.Tensor, h: torch.Tensor) -> None:
+    """h = x (float32) rounded to h's type."""
+    assert x.dtype == torch.float32 and x.shape == h.shape
+    _contig(x, "x"), _contig(h, "h")
+    _call("elementwise", "mb_cast_rows", [_vp, _vp, _i, _ll, _vp], _ptr(x), _ptr(h),
+          code_of(h.dtype), x.numel(), _stream())
+
+
+def unary_act(z: torch.Tensor, out: torch.Tensor, act: int,
+              table: Optional[torch.Tensor] = None, col0: int = 0,
+              ids: Optional[torch.Tensor] = None) -> None:
+    """out[t, c] = act(z[t, c]); with ``table`` [V, >= col0 + N] and ``ids`` int32 [T] also
+    times table[ids[t], col0 + c] (a factor that the token itself brings)."""
+    T, N = out.shape
+    assert z.shape == (T, N) and z.dtype == out.dtype and z.stride(1) == 1
+    _contig(out, "out")
+    if table is not None:
+        assert ids is not None and ids.dtype == torch.int32 and ids.numel() == T
+        assert table.dim() == 2 and table.stride(1) == 1 and table.shape[1] >= col0 + N
+    _call("elementwise", "mb_unary_act",
+          [_vp, _i, _vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _i, _vp],
+          _ptr(z), z.stride(0), _ptr(out), code_of(out.dtype), T, N, act, _ptr(table),
+          code_of(table.dtype) if table is not None else F32,
+          table.stride(0) if table is not None else 0, col0, _ptr(ids),
+          table.shape[0] if table is not None else 0, _stream())
+
+
+def softcap_rows(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) (float32, contiguous)."""
+    assert x.dtype == torch.float32
+    _contig(x, "x")
+    _call("elementwise", "mb_softcap", [_vp, _ll, _f, _vp], _ptr(x), x.numel(), float(cap),
+          _stream())
 
 
 def scale_rows(x: torch.Tensor, factor: float) -> None:
@@ -448,6 +509,33 @@ def mlstm_scan(z: torch.Tensor, cols, bi, bf, cap: float, q_scale: float, normw,
           float(q_scale), _ptr(normw), float(eps), _ptr(state), state.stride(0), state_off,
           _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), _ptr(raw), code_of(out.dtype), T,
           step.B, heads, dim, vdim, _stream(), launches=1 if step.B * heads >= 96 else 2)
+
+
+def retention_scan(z: torch.Tensor, cols, decay: torch.Tensor, k_scale: float,
+                   inv_freq: Optional[torch.Tensor], rot_dim: int, eps: float,
+                   state: torch.Tensor, step, out: torch.Tensor, heads: int, dim: int,
+                   vdim: int) -> None:
+    """Retention, token after token (csrc/recurrent.cu). z: the fused projection [T, ld]
+    float32; ``cols`` = the first columns of q, k, v and the output gate in it; ``decay``
+    float32 [heads] on the device. The state row of a slot holds heads x dim x vdim values."""
+    T = out.shape[0]
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and len(cols) == 4
+    assert decay.dtype == torch.float32 and decay.numel() == heads
+    if rot_dim > 0 and (inv_freq is None or inv_freq.dtype != torch.float32
+                        or inv_freq.numel() < rot_dim // 2):
+        raise KernelError(f"a rotation of {rot_dim} values without its frequencies")
+    _contig(out, "out")
+    assert out.shape == (T, heads * vdim) and state.dtype == torch.float32
+    assert state.stride(1) == 1 and state.shape[1] >= heads * dim * vdim
+    raw = torch.empty((T, heads * vdim), dtype=torch.float32, device=out.device)   # as in wkv_scan
+    _call("recurrent", "mb_retention_scan",
+          [_vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _i, _vp, _f, _vp, _ll, _ll, _vp, _vp, _vp, _vp,
+           _i, _i, _i, _i, _i, _i, _vp],
+          _ptr(z), z.stride(0), *[int(c) for c in cols], _ptr(decay), float(k_scale),
+          _ptr(inv_freq), rot_dim, _ptr(step.tok_pos), float(eps), _ptr(state), state.stride(0),
+          0, _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), _ptr(raw),
+          code_of(out.dtype), T, step.B, heads, dim, vdim, _stream(),
+          launches=1 if step.B * heads >= 96 else 2)
 
 
 # ------------------------------------------------------------------------------ latent attention
@@ -665,19 +753,24 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int =
 # ------------------------------------------------------------------------------ attention
 def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv, hd,
                    window: int, scale: float, vd: int = 0,
-                   sink: Optional[torch.Tensor] = None) -> None:
+                   sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                   gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
     """``vd``: the size of a value row when it differs from ``hd``. ``sink``: float32 [nh],
-    one more term exp(sink[h]) in the softmax denominators of head h."""
+    one more term exp(sink[h]) in the softmax denominators of head h. ``softcap`` > 0: scores
+    become softcap * tanh(score / softcap). ``gate``: logits of q's type, head h of token t at
+    ``gate[t * gate_stride + h]``; the head's output is multiplied by their sigmoid."""
     T = out.shape[0]
     _contig(out, "out")
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == nh)
+    assert gate is None or gate.dtype == out.dtype
     _call("attention_simt", "mb_attention_simt",
           [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
-           _i, _vp, _vp],
+           _i, _vp, _f, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           code_of(out.dtype), _ptr(line.page_table), line.max_pages, line.ring_pages,
           _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot), T, nh, nkv, hd,
-          window, float(scale), vd or hd, _ptr(sink), _stream())
+          window, float(scale), vd or hd, _ptr(sink), float(softcap), _ptr(gate), gate_stride,
+          _stream())
 
 
 # ------------------------------------------------------------------------------ sampling

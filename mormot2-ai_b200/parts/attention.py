@@ -7,7 +7,12 @@ head h reads KV head h div (heads div kv_heads) (``backend.cpu.pas:1253``).
 Options that a design may name: ``v_dim``, a value size that differs from the key size (the
 cache then keeps keys and values in pools of their own); ``names["sink"]``, a learned number
 per head whose exponential is one more term of the softmax denominator (a key with that
-score, not scaled, and a value of zero).
+score, not scaled, and a value of zero); ``softcap`` c > 0, which turns every scaled score s into
+c tanh(s / c) before the softmax; ``head_norm`` = "unit_after_rotation", which divides q and k
+by their root mean square (``head_norm_eps``) after the rotation, without a weight;
+``names["g"]``, a projection to one logit per head whose sigmoid multiplies the head's output
+before the output projection (its rows ride along in the q/k/v product); ``shared_kv``: the
+mixer has no key and value projections and only ever reads the cache line of another layer.
 """
 from __future__ import annotations
 
@@ -43,6 +48,18 @@ class GqaAttention(Part):
         self.qw, self.kvw, self.vw = self.nh * self.hd, self.nkv * self.hd, self.nkv * self.vd
         self.ow = self.nh * self.vd
         self.sink = None
+        self.softcap = float(p.get("softcap") or 0.0)
+        if self.softcap < 0:
+            raise ConfigError(f"a score cap of {self.softcap}")
+        self.head_norm = p.get("head_norm", "weighted_before_rotation")
+        if self.head_norm not in ("weighted_before_rotation", "unit_after_rotation"):
+            raise ConfigError(f"head norm \"{self.head_norm}\" is not known (known: "
+                              "unit_after_rotation, weighted_before_rotation)")
+        self.unit_after = self.head_norm == "unit_after_rotation"
+        if self.unit_after and ("q_norm" in self.names or self.head_norm_eps is None):
+            raise ConfigError("a unit norm after the rotation has an eps and no weights")
+        self.gate_n = self.nh if "g" in self.names else 0
+        self.shared_kv = bool(p.get("shared_kv", False))
 
     can_store = True      # forward(..., store=True) writes its output into x instead of adding
 
@@ -51,10 +68,13 @@ class GqaAttention(Part):
 
     def tensors(self) -> List[TensorNeed]:
         n = self.names
-        out = [TensorNeed(n["q"], (self.qw, self.hidden)),
-               TensorNeed(n["k"], (self.kvw, self.hidden)),
-               TensorNeed(n["v"], (self.vw, self.hidden)),
-               TensorNeed(n["o"], (self.hidden, self.ow))]
+        out = [TensorNeed(n["q"], (self.qw, self.hidden))]
+        if not self.shared_kv:
+            out += [TensorNeed(n["k"], (self.kvw, self.hidden)),
+                    TensorNeed(n["v"], (self.vw, self.hidden))]
+        out.append(TensorNeed(n["o"], (self.hidden, self.ow)))
+        if self.gate_n:
+            out.append(TensorNeed(n["g"], (self.nh, self.hidden)))
         if "sink" in n:
             out.append(TensorNeed(n["sink"], (self.nh,), "bias"))
         if "q_norm" in n:
@@ -67,18 +87,34 @@ class GqaAttention(Part):
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.rt = rt
-        plain = self.vd == self.hd and "sink" not in self.names
+        plain = (self.vd == self.hd and "sink" not in self.names and not self.softcap
+                 and not self.gate_n and not self.unit_after)
         if (plain and (self.hd % 16 or self.hd > 256)) or self.hd > 1024 or self.vd > 256:
             raise KernelError(
                 f"heads of {self.hd} values (value rows of {self.vd}) are not supported by the "
-                "attention kernels (a multiple of 16, at most 256; with a sink or value rows of "
-                "their own size any size up to 1024 and 256)")
+                "attention kernels (a multiple of 16, at most 256; with a sink, a score cap, a "
+                "gate per head or value rows of their own size any size up to 1024 and 256)")
         n = self.names
+        wg = weights[n["g"]] if self.gate_n else None
+        if self.shared_kv:
+            # queries (and the heads' gates) only: keys and values are another layer's
+            wq = weights[n["q"]]
+            if wg is not None and wg.dtype != wq.dtype:
+                wq, wg = wq.float(), wg.float()
+            self.qkv, self.split = None, None
+            self._q_only = Linear(torch.cat([wq, wg], dim=0) if wg is not None else wq, rt)
+            self.o = Linear(weights[n["o"]], rt)
+            self.q_norm = self.k_norm = None
+            return
         wq, wk, wv = weights[n["q"]], weights[n["k"]], weights[n["v"]]
+        if wg is not None and not (wq.dtype == wk.dtype == wv.dtype == wg.dtype):
+            wq, wk, wv, wg = wq.float(), wk.float(), wv.float(), wg.float()
         if wq.dtype == wk.dtype == wv.dtype:
-            # one product for q, k and v: the rows of the three weights one after another
-            self.qkv = Linear(torch.cat([wq, wk, wv], dim=0), rt)
-            self.q_only = Linear(self.qkv.weight[:self.qw], rt)
+            # one product for q, k and v: the rows of the three weights one after another (and
+            # behind them the rows of the heads' gates, where the design has them)
+            self.qkv = Linear(torch.cat([wq, wk, wv] + ([wg] if wg is not None else []), dim=0),
+                              rt)
+            self._q_only = None      # made when a run first reads another run's cache line
             self.split = None
             if getattr(rt, "consume_weights", False):
                 # the engine owns the tensors: the three originals go as soon as they are fused,
@@ -89,12 +125,22 @@ class GqaAttention(Part):
         else:
             self.qkv = None
             self.split = [Linear(wq, rt), Linear(wk, rt), Linear(wv, rt)]
-            self.q_only = self.split[0]
+            self._q_only = self.split[0]
         self.o = Linear(weights[n["o"]], rt)
         self.q_norm = weights.get(n.get("q_norm", ""))
         self.k_norm = weights.get(n.get("k_norm", ""))
         if "sink" in n:
             self.sink = weights[n["sink"]].to(torch.float32).contiguous()
+
+    @property
+    def q_only(self) -> Linear:
+        """The product for a run that reads keys and values another run wrote: q's rows (and
+        the gates') of the fused weight."""
+        if self._q_only is None:
+            w = self.qkv.weight
+            self._q_only = Linear(torch.cat([w[:self.qw], w[w.shape[0] - self.gate_n:]], dim=0)
+                                  if self.gate_n else w[:self.qw], self.rt)
+        return self._q_only
 
     def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
         """Adds the mixer's output into x, or returns it as ``Pending`` split sums for the next
@@ -102,23 +148,28 @@ class GqaAttention(Part):
         output instead of a sum onto it, or the split sums are returned and x is left as it is."""
         from .linear import Pending
         T = h.shape[0]
+        if writes_cache and self.shared_kv:
+            raise ConfigError("a mixer without key and value projections was asked to write "
+                              "a cache line")
         nkv = self.nkv if writes_cache else 0
-        width = self.qw + nkv * (self.hd + self.vd)
+        heads_width = self.qw + nkv * (self.hd + self.vd)
+        width = heads_width + self.gate_n
         eps = float(self.head_norm_eps) if self.head_norm_eps is not None else 0.0
         inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
                              else (None, 0))
         split_ok = (writes_cache and self.qkv is not None and rot_dim == self.hd
                     and self.hd in (64, 128, 256) and self.rt.dtype == torch.bfloat16
-                    and self.vd == self.hd)
+                    and self.vd == self.hd and not self.gate_n)
         qkv = self.qkv(h, defer=True) if split_ok else None
         if isinstance(qkv, Pending):
             # the kernel that norms and rotates q and k adds the split sums up as it reads them
             q = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
             K.qk_norm_rope_store(None, self.q_norm, self.k_norm, eps, inv_freq, rot_dim, step,
-                                 line, self.nh, nkv, self.hd, True, partial=qkv.partial, q_out=q)
+                                 line, self.nh, nkv, self.hd, True, partial=qkv.partial, q_out=q,
+                                 unit_after=self.unit_after)
             attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
             self.rt.attention(q, self.qw, attn, step, line, self.nh, self.nkv, self.hd,
-                              self.window, self.scale, sink=self.sink)
+                              self.window, self.scale, sink=self.sink, softcap=self.softcap)
             return self._project(attn, x, store)
         if qkv is not None:
             pass
@@ -132,10 +183,13 @@ class GqaAttention(Part):
             self.split[1](h, out=qkv[:, self.qw:self.qw + self.kvw])
             self.split[2](h, out=qkv[:, self.qw + self.kvw:])
         K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, eps, inv_freq, rot_dim,
-                             step, line, self.nh, nkv, self.hd, writes_cache, vd=self.vd)
+                             step, line, self.nh, nkv, self.hd, writes_cache, vd=self.vd,
+                             unit_after=self.unit_after)
         attn = torch.empty((T, self.ow), dtype=self.rt.dtype, device=h.device)
         self.rt.attention(qkv, width, attn, step, line, self.nh, self.nkv, self.hd,
-                          self.window, self.scale, vd=self.vd, sink=self.sink)
+                          self.window, self.scale, vd=self.vd, sink=self.sink,
+                          softcap=self.softcap,
+                          gate=qkv[:, heads_width:] if self.gate_n else None, gate_stride=width)
         return self._project(attn, x, store)
 
     def _project(self, attn, x, store: bool):

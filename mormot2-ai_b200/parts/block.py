@@ -14,6 +14,14 @@ at first). For each sublayer q with its vectors ``in``, ``out`` [S] and its matr
 x_t ← Σ_s mix[s, t] x_s + out[t] · y for all t at once. The write-back of one sublayer and the
 read (with its layer norm) of the next are one kernel (``csrc/streams.cu``), so a block hands
 its last write-back on as pending, as ``prenorm_residual`` hands on split sums.
+
+``output_norm_residual``: the norm stands on what a sublayer gives back, not on what it reads:
+x += norm_mixer(mixer(x)); x += norm_ff(feed_forward(x)). The sublayers read the residual
+itself, rounded to the activation type; the kernel that norms a sublayer's output and adds it
+into x also writes that rounding of the new x, which the next sublayer (or the next block, to
+which it is handed on as pending) reads. With ``side`` the block then adds an input of its own
+from the token: e = columns [col0, col0 + dim) of the row of a second embedding table,
+t = P (act(G x) * e), x += norm_side(t).
 """
 from __future__ import annotations
 
@@ -162,5 +170,115 @@ class HyperConnectionsBlock(Part):
         return StreamUpdate(self.w["feed_forward"]["mix"], self.w["feed_forward"]["out"], terms)
 
 
+class ReadyInput:
+    """The residual rounded to the activation type, already made by the block before (nothing
+    is owed to x)."""
+
+    def __init__(self, h):
+        self.h = h
+
+    def settle(self, x) -> None:
+        pass
+
+
+class OutputNormResidualBlock(Part):
+    capturable = True
+    accepts_pending = True
+
+    def __init__(self, spec, prefix: str = "", mixer=None, feed_forward=None, norms=None):
+        super().__init__(spec, prefix)
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+        for q, norm in norms.items():
+            if not hasattr(norm, "add_normed"):
+                raise ConfigError(f"the norm of \"{q}\" cannot norm a sublayer's output into the "
+                                  "residual (rmsnorm can)")
+        side = spec.params.get("side")
+        self.side = None
+        if side:
+            from .linear import Linear  # noqa: F401  (bound below)
+            from .. import kernels as K
+            self.side = dict(side)
+            if side["activation"] not in K.UNARY_ACTIVATIONS:
+                raise ConfigError(f"activation \"{side['activation']}\" is not known")
+            self.side_act = K.UNARY_ACTIVATIONS[side["activation"]]
+            self.side_names = {k: (v if k == "table" else prefix + v)
+                               for k, v in side["names"].items()}
+
+    def tensors(self):
+        if not self.side:
+            return []
+        sd, n = self.side, self.side_names
+        hidden, dim = int(sd["hidden_size"]), int(sd["dim"])
+        return [TensorNeed(n["table"], (int(sd["vocab_size"]), int(sd["table_width"])), "table"),
+                TensorNeed(n["gate"], (dim, hidden)), TensorNeed(n["proj"], (hidden, dim)),
+                TensorNeed(n["norm"], (hidden,), "vector")]
+
+    def bind(self, weights, rt) -> None:
+        self.rt = rt
+        if self.side:
+            from .linear import Linear
+            n = self.side_names
+            self.side_table = weights[n["table"]]
+            self.side_gate = Linear(weights[n["gate"]], rt)
+            self.side_proj = Linear(weights[n["proj"]], rt)
+            self.side_norm = weights[n["norm"]]
+
+    def _operand(self, x):
+        """The residual as the sublayers read it (on the 32-bit path: itself)."""
+        if self.rt.dtype == torch.float32:
+            return x
+        from .. import kernels as K
+        h = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        K.cast_rows(x, h)
+        return h
+
+    def _sublayer(self, part, h, args):
+        """The sublayer's output: float32 [T, hidden], or its split sums [parts, T, hidden]."""
+        y = torch.empty((h.shape[0], h.shape[1]), dtype=torch.float32, device=h.device)
+        if getattr(part, "can_store", False):
+            pending = part.forward(h, y, *args, store=True)
+            return pending.partial if pending is not None else y
+        y.zero_()
+        pending = part.forward(h, y, *args)
+        if pending is not None:
+            settle(y, pending)
+        return y
+
+    def _next_operand(self, x):
+        return None if self.rt.dtype == torch.float32 else \
+            torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+
+    def forward(self, x, step, line, state, writes_cache: bool, pending=None):
+        from .. import kernels as K
+        if isinstance(pending, ReadyInput):
+            h = pending.h
+        else:
+            if pending is not None:
+                settle(x, pending)
+            h = self._operand(x)
+        y = self._sublayer(self.mixer, h, (step, line, state, writes_cache))
+        h_next = self._next_operand(x)
+        self.norms["mixer"].add_normed(y, x, h_next)
+        h = h_next if h_next is not None else x
+        if "feed_forward" in self.norms:
+            y = self._sublayer(self.feed_forward, h, (step,))
+            h_next = self._next_operand(x)
+            self.norms["feed_forward"].add_normed(y, x, h_next)
+            h = h_next if h_next is not None else x
+        if self.side:
+            sd = self.side
+            z = self.side_gate(h)
+            g = torch.empty_like(z)
+            K.unary_act(z, g, self.side_act, self.side_table, int(sd["col0"]), step.tok_ids)
+            from .linear import Pending
+            t = self.side_proj(g, out_dtype=torch.float32, defer=True)
+            h_next = self._next_operand(x)
+            K.norm_add(t.partial if isinstance(t, Pending) else t, self.side_norm,
+                       float(sd["eps"]), x, h_next)
+            h = h_next if h_next is not None else x
+        return ReadyInput(h) if h is not x else None
+
+
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)
+BLOCKS.register("output_norm_residual", OutputNormResidualBlock)
 BLOCKS.register("hyper_connections", HyperConnectionsBlock)

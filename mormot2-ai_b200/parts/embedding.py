@@ -1,7 +1,8 @@
 """Token embedding (rows of the table into the float32 residual, times ``scale`` where a
 design names one; the reference scales nothing: ``decoder.pas:3292-3309``) and the head (logits = h · Headᵀ in float32, the
 head being the embedding when tied: ``model.qwen3.pas:555-579``; a head with ``scale``
-multiplies its float32 logits by that constant)."""
+multiplies its float32 logits by that constant; one with ``softcap`` c turns them into
+c tanh(logits / c))."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -44,6 +45,7 @@ class LmHead(Part):
         self.stored_name = p["name"]
         self.vocab, self.hidden = int(p["vocab_size"]), int(p["hidden_size"])
         self.scale = float(p.get("scale", 1.0))
+        self.softcap = float(p.get("softcap") or 0.0)    # logits <- c tanh(logits / c)
 
     def tensors(self) -> List[TensorNeed]:
         if self.tied:
@@ -59,6 +61,8 @@ class LmHead(Part):
         logits = self.linear(h, out_dtype=torch.float32)
         if self.scale != 1.0:
             K.scale_rows(logits, self.scale)
+        if self.softcap > 0:
+            K.softcap_rows(logits, self.softcap)
         return logits
 
 

@@ -8,6 +8,8 @@ the last product then accumulates onto, by the norm before the feed-forward wher
 can (``residual_bias``), else by a kernel of its own. On the 32-bit path the product stores
 gate and up and one kernel adds the biases, applies the activation and places b_d.
 ``none``: a layer without a feed-forward.
+``mlp``: W_d act(W_u h) without a gate and without biases, ``activation`` "relu_squared"
+(max(z, 0)²), "silu" or "gelu_tanh".
 
 SwiGLU feed-forward: x += (silu(h·Wgᵀ) · (h·Wuᵀ)) · Wdᵀ, no bias
 (``decoder.pas:2865-2899``, ``backend.cpu.pas:1827-1833`` of the reference). Gate and up are
@@ -138,6 +140,45 @@ class GatedMlp(Part):
         return out if isinstance(out, Pending) else None
 
 
+class PlainMlp(Part):
+    capturable = True
+    can_store = True      # forward(..., store=True) writes its output into x instead of adding
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        if p["activation"] not in K.UNARY_ACTIVATIONS:
+            raise ConfigError(f"activation \"{p['activation']}\" is not known "
+                              f"(known: {', '.join(sorted(K.UNARY_ACTIVATIONS))})")
+        self.act = K.UNARY_ACTIVATIONS[p["activation"]]
+        self.names = {k: prefix + v for k, v in p["names"].items()}
+
+    def tensors(self) -> List[TensorNeed]:
+        n = self.names
+        return [TensorNeed(n["up"], (self.inter, self.hidden)),
+                TensorNeed(n["down"], (self.hidden, self.inter))]
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        self.up = Linear(weights[self.names["up"]], rt)
+        self.down = Linear(weights[self.names["down"]], rt)
+
+    def forward(self, h, x, step, store: bool = False):
+        """Adds the feed-forward's output into x (``store``: writes it there), or returns it as
+        ``Pending`` split sums for whoever reads it next (x is then not touched)."""
+        from .linear import Pending
+        z = self.up(h)
+        act = torch.empty_like(z)
+        K.unary_act(z, act, self.act)
+        if store:
+            out = self.down(act, out=x, defer=True)
+        else:
+            out = self.down(act, add_into=x, defer=True)
+        return out if isinstance(out, Pending) else None
+
+
 class NoFeedForward(Part):
     capturable = True
 
@@ -148,3 +189,4 @@ class NoFeedForward(Part):
 FEED_FORWARDS.register("swiglu", SwiGluFfn)
 FEED_FORWARDS.register("gated_mlp", GatedMlp)
 FEED_FORWARDS.register("none", NoFeedForward)
+FEED_FORWARDS.register("mlp", PlainMlp)

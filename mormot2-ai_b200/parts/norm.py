@@ -45,6 +45,11 @@ class RmsNorm(Part):
                   pending.partial if pending is not None else None)
         return out
 
+    def add_normed(self, y: torch.Tensor, x: torch.Tensor, h: Optional[torch.Tensor] = None) -> None:
+        """x += w · y / rms(y) for a sublayer's output y [T, size] float32 (or its split sums
+        [parts, T, size]); ``h`` receives the new x in the activation type."""
+        K.norm_add(y, self.weight, self.eps, x, h)
+
 
 class DynamicTanh(Part):
     """``name`` is the weight; the scalar and the shift are stored beside it as

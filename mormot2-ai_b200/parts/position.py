@@ -4,7 +4,9 @@ product inv_freq[i] · pos.
 
 ``rope_half`` is the rotary encoding in the rotate-half pairing (i, i + rot_dim/2) with
 inv_freq[i] = 1 / f32(theta ^ f32(2i / rot_dim)), each step rounded to float32 as the
-reference does (``decoder.pas:1733-1736``; angles ``:2539-2561``). ``none`` rotates nothing.
+reference does (``decoder.pas:1733-1736``; angles ``:2539-2561``); with ``rounding`` = "once"
+the frequencies theta^(−2i / rot_dim) are formed in float64 and rounded to float32 once.
+``none`` rotates nothing.
 
 ``rope_yarn`` is the same rotation with YaRN's frequencies: with
 d(t) = dims · ln(original / (2π t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
@@ -50,11 +52,18 @@ class RopeHalf(Part):
         self.rot_dim = int(spec.params["rot_dim"])
         if self.rot_dim <= 0 or self.rot_dim % 2:
             raise ConfigError(f"a rotary encoding over {self.rot_dim} values of a head")
+        self.rounding = spec.params.get("rounding", "stepwise")
+        if self.rounding not in ("stepwise", "once"):
+            raise ConfigError(f"rounding \"{self.rounding}\" of the frequencies (stepwise, once)")
         self.inv_freq: Optional[torch.Tensor] = None
 
     def bind(self, weights, rt) -> None:
-        self.inv_freq = torch.from_numpy(
-            rope_inverse_frequencies(self.theta, self.rot_dim)).to(rt.device)
+        if self.rounding == "once":
+            i = np.arange(self.rot_dim // 2, dtype=np.float64)
+            f = np.exp(-np.log(self.theta) * 2.0 * i / self.rot_dim).astype(np.float32)
+        else:
+            f = rope_inverse_frequencies(self.theta, self.rot_dim)
+        self.inv_freq = torch.from_numpy(f).to(rt.device)
 
     def frequencies(self) -> Tuple[Optional[torch.Tensor], int]:
         return self.inv_freq, self.rot_dim

@@ -17,6 +17,12 @@ with a running maximum m (from 0): m' = max(f + m, i), S ← e^(f+m−m') S + e^
 likewise with k, o = Sᵀ q / (max(|n·q|, e^(−m')) + 1e-6) with q scaled by dim^(−1/2); each
 head's o over its root mean square, times ``norm``, times sigmoid(W_g h), then W_o. q, k, v,
 the output gate and both gates are one product.
+
+``retention`` — linear attention with a constant decay d per head and no softmax or
+denominator: q and k (heads × dim) turn by the token's position (``position``), k is then
+multiplied by dim^(−1/2); S ← d S + k vᵀ (dim × vdim), o = Sᵀ q with the state that already
+holds the token; each head's o over its root mean square (no weight), times silu(W_g h), then
+W_o. q, k, v and the gate are one product.
 """
 from __future__ import annotations
 
@@ -187,5 +193,71 @@ class MlstmMixer(Part):
         return _project(self.o, y, x, store)
 
 
+class RetentionMixer(Part):
+    capturable = True
+    can_store = True
+
+    def __init__(self, spec, prefix: str = "", positions=None):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.nh = int(p["hidden_size"]), int(p["heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.eps = float(p["eps"])
+        self.decay = [float(d) for d in p["decay"]]
+        if len(self.decay) != self.nh:
+            raise ConfigError(f"{len(self.decay)} decays for {self.nh} heads")
+        self.position = (positions or {}).get(p.get("position", ""))
+        if p.get("position") and self.position is None:
+            raise ConfigError(f"the mixer names the position encoding \"{p['position']}\", "
+                              "which the model does not define")
+        self.names = {k: prefix + v for k, v in p["names"].items()}
+        staged = 2 * self.dim + (2 + _scan_parts(self.vdim)) * self.vdim
+        if _scan_smem(self.dim, self.vdim, staged) > 200 * 1024:
+            raise ConfigError(f"a retention state of {self.dim} x {self.vdim} values per head is "
+                              "more than the kernel keeps on one multiprocessor")
+
+    def libraries(self, rt) -> List[str]:
+        return ["recurrent"]
+
+    def tensors(self) -> List[TensorNeed]:
+        n, W, H = self.names, self.hidden, self.nh
+        return [TensorNeed(n["q"], (H * self.dim, W)), TensorNeed(n["k"], (H * self.dim, W)),
+                TensorNeed(n["v"], (H * self.vdim, W)), TensorNeed(n["g"], (H * self.vdim, W)),
+                TensorNeed(n["o"], (W, H * self.vdim))]
+
+    def state_need(self) -> StateNeed:
+        return StateNeed((self.nh * self.dim * self.vdim,), "float32", 0.0)
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        n = self.names
+        ws = [weights[n[s]] for s in ("q", "k", "v", "g")]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.cols, at = [], 0
+        for w in ws:
+            self.cols.append(at)
+            at += w.shape[0]
+        self.fused = Linear(torch.cat(ws, dim=0), rt)
+        if getattr(rt, "consume_weights", False):
+            del ws
+            for s in ("q", "k", "v", "g"):
+                weights.pop(n[s], None)
+        self.decay_dev = torch.tensor(self.decay, dtype=torch.float32, device=rt.device)
+        self.o = Linear(weights[n["o"]], rt)
+
+    def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
+        T = h.shape[0]
+        # what enters the recurrence leaves its product as float32 and is never rounded
+        z = self.fused(h, out_dtype=torch.float32)
+        inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
+                             else (None, 0))
+        y = torch.empty((T, self.nh * self.vdim), dtype=self.rt.dtype, device=h.device)
+        K.retention_scan(z, self.cols, self.decay_dev, self.dim ** -0.5, inv_freq, rot_dim,
+                         self.eps, state, step, y, self.nh, self.dim, self.vdim)
+        return _project(self.o, y, x, store)
+
+
 MIXERS.register("wkv", WkvMixer)
+MIXERS.register("retention", RetentionMixer)
 MIXERS.register("mlstm", MlstmMixer)
