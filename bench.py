@@ -1,7 +1,7 @@
 """Measures decoding and prefill of the Qwen3-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design busavik|fimudra [--sizes small,mid]   (another workload, see below)
+    python bench.py --design busavik|fimudra|sezopel [--sizes small,mid]   (another workload, see below)
 
 A step is one decode step of a batch of 8 sequences whose context reaches 4,096 at the end of
 the timed steps. ``value`` is decoded tokens a second with the steps running back to back on
@@ -23,7 +23,9 @@ attention, Dynamic Tanh, routed experts) at layer sizes of real models beside th
 of equal size: prefill and decode tokens/s, and the kernels of a step by class against what
 each class must compute or read. ``--design fimudra`` does the same for the Fimudra design
 (residual streams, attention with a sink beside a gated matrix memory, a decaying matrix
-state, routed experts with identity experts).
+state, routed experts with identity experts), ``--design sezopel`` for the Sezopel design
+(attention with capped scores, unit-norm heads and head gates, a layer that reads another's
+keys and values, retention, normed sublayer outputs, an input from the token after every layer).
 """
 import argparse
 import json
@@ -412,6 +414,75 @@ def fimudra_shapes(name):
     return FimudraConfig.from_dict(doc), twin
 
 
+def sezopel_shapes(name):
+    """A Sezopel configuration whose layers have the sizes of a real model's (an attention layer
+    with keys and values of its own, one that reads them, and a retention layer with value rows
+    twice its keys; dense feed-forwards of two matrices; an input from the token after every
+    layer) and the Qwen3 configuration of equal width, head count, KV heads, head size and layer
+    count whose gated feed-forward of three matrices has as many weights, the closest model
+    of this library."""
+    from mormot2_ai_b200 import Qwen3Config, SezopelConfig
+    sizes = {
+        # width, heads, kv heads, dim, retention heads, retention dim, retention vdim, ff, side
+        "small": (1024, 8, 2, 64, 8, 64, 128, 6144, 128),
+        "mid": (2048, 16, 4, 128, 16, 64, 128, 12288, 256),
+    }[name]
+    w, h, kv, dim, rh, rd, rv, ff, side = sizes
+    vocab = 32768
+    att = {"heads": h, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5 * 8.0,
+           "softcap": 50.0, "rot": {"base": 1e6, "dims": dim}}
+    ret = {"heads": rh, "dim": rd, "vdim": rv, "rot": {"base": 1e4, "dims": rd},
+           "decay": [1.0 - 2.0 ** (-5 - 7 * i / max(1, rh - 1)) for i in range(rh)]}
+    mlp = {"kind": "dense", "ff": ff}
+    doc = {"architecture": "Sezopel", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
+           "embedding": {"scale": w ** 0.5}, "logit_softcap": 30.0, "token_side": {"dim": side},
+           "layers": [{"type": "attention", "mixer": att, "mlp": mlp},
+                      {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": mlp},
+                      {"type": "retention", "mixer": ret, "mlp": mlp}]}
+    twin = Qwen3Config(vocab_size=vocab, hidden_size=w, num_hidden_layers=3,
+                       num_attention_heads=h, num_key_value_heads=kv, head_dim=dim,
+                       intermediate_size=2 * ff // 3, max_position_embeddings=40960,
+                       rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+    return SezopelConfig.from_dict(doc), twin
+
+
+def sezopel_work(cfg, tokens, batch, held):
+    """As ``busavik_work`` for the Sezopel family: attention counts both products over the
+    causal pairs (a decode step the keys and values it reads, once per layer that reads them),
+    the recurrences the multiply-adds of the state's update and read (a decode step the state
+    read and written), the products every matrix (the token's input included: its table row
+    is a gather and not counted)."""
+    pairs = tokens * (tokens + 1) / 2
+    out = {"prefill_flops": {"attention": 0.0, "products": 0.0, "recurrence": 0.0},
+           "decode_bytes": {"attention": 0.0, "products": 0.0, "recurrence": 0.0}}
+    w = cfg.width
+    for layer in cfg.layers:
+        m, mlp = layer["mixer"], layer.get("mlp")
+        dim = m["dim"]
+        vd = m.get("vdim") or dim
+        if layer["type"] == "attention":
+            h, kv = m["heads"], m.get("kv_heads") or m["heads"]
+            dense = (h * dim + h + h * vd) * w
+            if m.get("kv_from") is None:
+                dense += kv * (dim + vd) * w
+            out["prefill_flops"]["attention"] += 2 * h * (dim + vd) * pairs
+            out["decode_bytes"]["attention"] += 2 * held * kv * (dim + vd)
+        else:
+            h = m["heads"]
+            dense = (2 * h * dim + 3 * h * vd) * w
+            out["prefill_flops"]["recurrence"] += tokens * 4 * h * dim * vd
+            out["decode_bytes"]["recurrence"] += batch * 2 * 4 * h * dim * vd
+        if mlp:
+            dense += 2 * w * mlp["ff"]
+        if cfg.side_dim:
+            dense += 2 * w * cfg.side_dim
+        out["prefill_flops"]["products"] += 2 * tokens * dense
+        out["decode_bytes"]["products"] += 2 * dense
+    out["prefill_flops"]["products"] += 2 * cfg.vocab * w
+    out["decode_bytes"]["products"] += 2 * cfg.vocab * w
+    return out
+
+
 def fimudra_work(cfg, tokens, batch, held, experts_read=None):
     """As ``busavik_work`` for the Fimudra family, with a class of its own for the recurrences:
     a prefill's recurrences count the multiply-adds of the state's update and of its read
@@ -465,6 +536,8 @@ def busavik_work(cfg, tokens, batch, held, experts_read=None):
     random weights the tokens of a batch choose much the same ones), else the most possible."""
     if hasattr(cfg, "streams"):
         return fimudra_work(cfg, tokens, batch, held, experts_read)
+    if hasattr(cfg, "side_dim"):
+        return sezopel_work(cfg, tokens, batch, held)
     pairs = tokens * (tokens + 1) / 2
     out = {"prefill_flops": {"attention": 0.0, "products": 0.0},
            "decode_bytes": {"attention": 0.0, "products": 0.0}}
@@ -514,7 +587,7 @@ def busavik_bench(a):
     steps, warm = min(a.steps, 64), max(a.warmup, 3)
     points = {}
     for size in [v for v in a.sizes.split(",") if v]:
-        shapes = fimudra_shapes if a.design == "fimudra" else busavik_shapes
+        shapes = {"fimudra": fimudra_shapes, "sezopel": sezopel_shapes}.get(a.design, busavik_shapes)
         for family, cfg in zip((a.design, "qwen3"), shapes(size)):
             eng = Engine.from_random(cfg, seed=5, std=0.02, max_tokens=batch * ctx + tokens,
                                      max_context=max(ctx, tokens), max_slots=batch,
@@ -593,8 +666,8 @@ def main():
                     help="token counts of the long prefill points (one sequence each)")
     ap.add_argument("--only-prefill", type=int, nargs="?", const=PREFILL_TOKENS, default=0,
                     help="only a prefill of this many tokens (for profiles; prints a short line)")
-    ap.add_argument("--design", default="", choices=["", "busavik", "fimudra"],
-                    help="busavik, fimudra: instead of the default workload, prefill and decode "
+    ap.add_argument("--design", default="", choices=["", "busavik", "fimudra", "sezopel"],
+                    help="busavik, fimudra, sezopel: instead of the default workload, prefill and decode "
                          "of that design at layer sizes of real models beside the Qwen3 model of "
                          "equal size (prints its own JSON line)")
     ap.add_argument("--sizes", default="small,mid", help="with --design: which layer sizes")

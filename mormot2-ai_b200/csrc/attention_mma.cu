@@ -16,6 +16,11 @@
 // the head dimension (for q·k) and over the keys (for p·v) does not care about order, so the
 // fragments use a permutation of the dimensions under which every thread's values lie
 // contiguous in memory.
+//
+// Every kernel takes a cap on the scores (`softcap` > 0: s <- c tanh(s / c) after the scale, a
+// template parameter of the kernels so that models without one run the code they ran before)
+// and a gate (`gate` not null: head h of token t at gate[t * gate_stride + h], a logit whose
+// sigmoid multiplies the head's output where it is written).
 #include "mma_common.cuh"
 #include "tc_common.cuh"
 
@@ -24,6 +29,17 @@ MB_DEFINE_LAST_ERROR
 typedef __nv_bfloat16 bf16;
 
 #define DEC_WARPS 4
+
+// A raw score in the exponent's base-2 units. Without a cap `pre` = scale log2(e); with one
+// `pre` = 2 log2(e) scale / c and `cap_log2` = c log2(e).
+template <bool CAP>
+__device__ __forceinline__ float score_log2(float s, float pre, float cap_log2) {
+  return CAP ? cap_log2 * tanh_of_2xlog2e(s * pre) : s * pre;
+}
+__device__ __forceinline__ float gate_of(const bf16* gate, int gate_stride, int t, int h) {
+  return gate == nullptr ? 1.0f
+                         : sigmoid_f32(__bfloat162float(gate[(size_t)t * gate_stride + h]));
+}
 
 // scores of one page: sc[u][e] = q(row) · k(key) for the keys u*8 + 2c + (e & 1) of the page and
 // the rows r (e < 2) and r + 8 (e >= 2) of the warp's 16 query rows
@@ -115,7 +131,7 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
 // pages of this split (every `splits`-th page of the sequence) into shared memory, a whole K
 // tile and a whole V tile per page (16 KB each for heads of 128) by bulk asynchronous copies,
 // three pages ahead. Warps 0-3 take 16 keys of every page each.
-template <int HD>
+template <int HD, bool CAP>
 __global__ void __launch_bounds__((DEC_WARPS + 1) * 32, 2)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kpool,
                    const bf16* __restrict__ vpool, const int* __restrict__ page_table,
@@ -123,7 +139,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ tok_pos, int nh,
                    int nkv, int window, float scale_log2, float* __restrict__ part_o,
                    float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
-                   int in_clusters, int* __restrict__ error, const float* __restrict__ sink) {
+                   int in_clusters, int* __restrict__ error, const float* __restrict__ sink,
+                   float cap_log2, const bf16* __restrict__ gate, int gate_stride) {
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
@@ -238,8 +255,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + u * 8 + 2 * c + e;
           const bool ok = key >= lo && key <= pos;
-          sc[u][e] = ok ? sc[u][e] * scale_log2 : -INFINITY;
-          sc[u][2 + e] = ok ? sc[u][2 + e] * scale_log2 : -INFINITY;
+          sc[u][e] = ok ? score_log2<CAP>(sc[u][e], scale_log2, cap_log2) : -INFINITY;
+          sc[u][2 + e] = ok ? score_log2<CAP>(sc[u][2 + e], scale_log2, cap_log2) : -INFINITY;
           mx0 = fmaxf(mx0, sc[u][e]);
           mx1 = fmaxf(mx1, sc[u][2 + e]);
         }
@@ -348,7 +365,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         part_ml[at * 2 + 1] = L;
       }
     } else if (S == 1) {
-      out[(size_t)t * out_stride + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
+      out[(size_t)t * out_stride + (size_t)(h0 + row) * HD + d] =
+          __float2bfloat16_rn(acc / L * gate_of(gate, gate_stride, t, h0 + row));
     } else {
       sm_c[row * HD + d] = acc;
       if (d == 0) {
@@ -378,7 +396,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         L += l * f;
         acc += v * f;
       }
-      out[(size_t)t * out_stride + (size_t)(h0 + row) * HD + d] = __float2bfloat16_rn(acc / L);
+      out[(size_t)t * out_stride + (size_t)(h0 + row) * HD + d] =
+          __float2bfloat16_rn(acc / L * gate_of(gate, gate_stride, t, h0 + row));
     }
     cluster_sync_all();  // no CTA leaves while another may still read its shared memory
   }
@@ -389,7 +408,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o,
                                   const float* __restrict__ part_ml, int S, bf16* __restrict__ out,
-                                  int out_stride, int nh) {
+                                  int out_stride, int nh, const bf16* __restrict__ gate,
+                                  int gate_stride) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
@@ -404,7 +424,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o,
     L += part_ml[(at + s) * 2 + 1] * f;
     acc += part_o[(at + s) * HD + d] * f;
   }
-  out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc / L);
+  out[(size_t)t * out_stride + (size_t)h * HD + d] =
+      __float2bfloat16_rn(acc / L * gate_of(gate, gate_stride, t, h));
 }
 
 // floats of scratch that mb_attention_decode needs for T tokens
@@ -433,37 +454,46 @@ static int decode_launch(const void* q, int q_stride, void* out, int out_stride,
                          int max_pages, int ring_pages, const int* tok_slot, const int* tok_pos,
                          int T, int nh, int nkv, int hd, int window, float scale, int splits,
                          float* part_o, float* part_ml, int in_clusters, int* error,
-                         cudaStream_t s, const float* sink = nullptr) {
+                         cudaStream_t s, const float* sink = nullptr, float softcap = 0.f,
+                         const void* gate = nullptr, int gate_stride = 0) {
   const int G = nh / nkv, subs = (G + 15) / 16;
-  const float scale_log2 = scale * 1.4426950408889634f;
+  const float log2e = 1.4426950408889634f;
+  const float scale_log2 = softcap > 0.f ? 2.f * log2e * scale / softcap : scale * log2e;
+  const float cap_log2 = softcap * log2e;
   dim3 grid(splits, nkv * subs, T), mgrid(T, nh);
-#define GO(HD_)                                                                                \
+#define GO(HD_, CAP_)                                                                          \
   {                                                                                            \
     constexpr int smem = DEC_STAGES * 2 * MB_PAGE * HD_ * 2 + 64;                              \
     static bool configured = false;                                                            \
     if (!configured) {                                                                         \
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD_>,                            \
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<HD_, CAP_>,                      \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       if (e != cudaSuccess) MB_FAIL("mb_attention_decode: %s", cudaGetErrorString(e));         \
       configured = true;                                                                       \
     }                                                                                          \
     if (in_clusters && splits > 1) {                                                           \
-      mb_launch_clusters(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,   \
-                         splits, (const bf16*)q, q_stride, (const bf16*)kpool,                 \
+      mb_launch_clusters(attn_decode_kernel<HD_, CAP_>, grid, dim3((DEC_WARPS + 1) * 32),      \
+                         smem, s, splits, (const bf16*)q, q_stride, (const bf16*)kpool,        \
                          (const bf16*)vpool, page_table, max_pages, ring_pages, tok_slot,      \
                          tok_pos, nh, nkv, window, scale_log2, part_o, part_ml, (bf16*)out,    \
-                         out_stride, 1, error, sink);                                          \
+                         out_stride, 1, error, sink, cap_log2, (const bf16*)gate, gate_stride);\
     } else {                                                                                   \
-      mb_launch(attn_decode_kernel<HD_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,            \
+      mb_launch(attn_decode_kernel<HD_, CAP_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,      \
                 (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,  \
                 max_pages, ring_pages, tok_slot, tok_pos, nh, nkv, window, scale_log2, part_o, \
-                part_ml, (bf16*)out, out_stride, in_clusters, error, sink);                    \
+                part_ml, (bf16*)out, out_stride, in_clusters, error, sink, cap_log2,           \
+                (const bf16*)gate, gate_stride);                                               \
       if (!in_clusters)                                                                        \
         mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,        \
-                  (const float*)part_ml, splits, (bf16*)out, out_stride, nh);                  \
+                  (const float*)part_ml, splits, (bf16*)out, out_stride, nh,                   \
+                  (const bf16*)gate, gate_stride);                                             \
     }                                                                                          \
   }
-  if (hd == 64) GO(64) else GO(128)
+  if (softcap > 0.f) {
+    if (hd == 64) GO(64, true) else GO(128, true)
+  } else {
+    if (hd == 64) GO(64, false) else GO(128, false)
+  }
 #undef GO
   MB_CHECK_LAUNCH("mb_attention_decode");
 }
@@ -481,6 +511,7 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
                                   const int* tok_pos, int T, int nh, int nkv,
                                   int hd, int window, float scale, int splits, float* scratch,
                                   long long scratch_floats, int* error, const float* sink,
+                                  float softcap, const void* gate, int gate_stride,
                                   void* stream) {
   if (T <= 0) return 0;
   if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
@@ -490,7 +521,7 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
   return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                        ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
                        scratch, scratch + (size_t)T * nh * splits * hd, 0, error,
-                       (cudaStream_t)stream, sink);
+                       (cudaStream_t)stream, sink, softcap, gate, gate_stride);
 }
 
 // The same with the splits of a (token, group of heads) as the CTAs of one thread-block
@@ -504,6 +535,7 @@ MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* ou
                                            const int* tok_slot, const int* tok_pos, int T,
                                            int nh, int nkv, int hd, int window, float scale,
                                            int splits, int* error, const float* sink,
+                                           float softcap, const void* gate, int gate_stride,
                                            void* stream) {
   if (T <= 0) return 0;
   if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
@@ -513,7 +545,8 @@ MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* ou
   if (((uintptr_t)out & 1)) MB_FAIL("mb_attention_decode_clusters: out is not aligned");
   return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                        ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
-                       nullptr, nullptr, 1, error, (cudaStream_t)stream, sink);
+                       nullptr, nullptr, 1, error, (cudaStream_t)stream, sink, softcap, gate,
+                       gate_stride);
 }
 
 // ------------------------------------------------------------------ prefill
@@ -584,14 +617,15 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 // asynchronous copies, two pages ahead of the page in work. The rows of a tile are padded in
 // shared memory (keys to a pitch of 2 HD + 64 bytes, values to 2 HD + 16), which makes every
 // fragment read of qk_page_smem / pv_page_smem free of bank conflicts.
-template <int HD>
+template <int HD, bool CAP>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 2)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                     int out_stride, const bf16* __restrict__ kpool,
                     const bf16* __restrict__ vpool, const int* __restrict__ page_table,
                     int max_pages, int ring_pages, const int* __restrict__ seq_start,
                     const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
-                    int nkv, int window, float scale_log2, const float* __restrict__ sink) {
+                    int nkv, int window, float scale_log2, const float* __restrict__ sink,
+                    float cap_log2, const bf16* __restrict__ gate, int gate_stride) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int CH = HD / 32, DB = HD / 64;
@@ -684,8 +718,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + u * 8 + 2 * c + e;
-          sc[u][e] = (key >= la && key <= pa) ? sc[u][e] * scale_log2 : -INFINITY;
-          sc[u][2 + e] = (key >= lb && key <= pb) ? sc[u][2 + e] * scale_log2 : -INFINITY;
+          sc[u][e] = (key >= la && key <= pa) ? score_log2<CAP>(sc[u][e], scale_log2, cap_log2)
+                                              : -INFINITY;
+          sc[u][2 + e] = (key >= lb && key <= pb)
+                             ? score_log2<CAP>(sc[u][2 + e], scale_log2, cap_log2) : -INFINITY;
           mx0 = fmaxf(mx0, sc[u][e]);
           mx1 = fmaxf(mx1, sc[u][2 + e]);
         }
@@ -731,7 +767,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+  const float i0 = (has_a ? gate_of(gate, gate_stride, start + ra, h) : 1.0f) / l0;
+  const float i1 = (has_b ? gate_of(gate, gate_stride, start + rb, h) : 1.0f) / l1;
   // a thread holds the dims db*64 + 16c .. + 15 of its two rows
 #pragma unroll
   for (int db = 0; db < DB; ++db) {
@@ -764,7 +801,8 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
                                    int max_pages, int ring_pages, const int* seq_start,
                                    const int* seq_past, const int* seq_slot, int B, int max_new,
                                    int nh, int nkv, int hd, int window, float scale, int* error,
-                                   const float* sink, void* stream) {
+                                   const float* sink, float softcap, const void* gate,
+                                   int gate_stride, void* stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (hd != 64 && hd != 128)
     MB_FAIL("mb_attention_prefill: heads of %d values are not supported (64 or 128)", hd);
@@ -775,23 +813,30 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
   if (B > 65535 || nh > 65535) MB_FAIL("mb_attention_prefill: %d sequences, %d heads", B, nh);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid((max_new + 63) / 64, nh, B);
-  const float scale_log2 = scale * 1.4426950408889634f;
-#define GO(HD_)                                                                                \
+  const float log2e = 1.4426950408889634f;
+  const float scale_log2 = softcap > 0.f ? 2.f * log2e * scale / softcap : scale * log2e;
+  const float cap_log2 = softcap * log2e;
+#define GO(HD_, CAP_)                                                                          \
   {                                                                                            \
     constexpr int smem = PRE_STAGES * MB_PAGE * (4 * HD_ + 80);                                \
     static bool configured = false;                                                            \
     if (!configured) {                                                                         \
-      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD_>,                           \
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HD_, CAP_>,                     \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
       if (e != cudaSuccess) MB_FAIL("mb_attention_prefill: %s", cudaGetErrorString(e));        \
       configured = true;                                                                       \
     }                                                                                          \
-    mb_launch(attn_prefill_kernel<HD_>, grid, dim3(DEC_WARPS * 32), smem, s, (const bf16*)q,   \
-              q_stride, (bf16*)out, out_stride, (const bf16*)kpool, (const bf16*)vpool,        \
-              page_table, max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv,       \
-              window, scale_log2, sink);                                                       \
+    mb_launch(attn_prefill_kernel<HD_, CAP_>, grid, dim3(DEC_WARPS * 32), smem, s,             \
+              (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool,            \
+              (const bf16*)vpool, page_table, max_pages, ring_pages, seq_start, seq_past,      \
+              seq_slot, nh, nkv, window, scale_log2, sink, cap_log2, (const bf16*)gate,        \
+              gate_stride);                                                                    \
   }
-  if (hd == 64) GO(64) else GO(128)
+  if (softcap > 0.f) {
+    if (hd == 64) GO(64, true) else GO(128, true)
+  } else {
+    if (hd == 64) GO(64, false) else GO(128, false)
+  }
 #undef GO
   (void)error;
   MB_CHECK_LAUNCH("mb_attention_prefill");
@@ -840,5 +885,6 @@ MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out,
   return mb_attention_decode(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                              ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window,
                              scale, splits, g_static_scratch_ptr[device],
-                             MB_ATTENTION_DECODE_STATIC_FLOATS, error, nullptr, stream);
+                             MB_ATTENTION_DECODE_STATIC_FLOATS, error, nullptr, 0.f, nullptr, 0,
+                             stream);
 }

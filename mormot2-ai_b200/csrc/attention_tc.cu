@@ -166,6 +166,10 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
       : "memory");
 }
 
+// CAP: the scores are capped, s <- c tanh(s scale / c): `scale_log2` is then 2 log2(e) scale / c
+// and `cap_log2` = c log2(e). `gate` (may be null): head h of token t at
+// gate[t * gate_stride + h], a logit whose sigmoid multiplies the head's output.
+template <bool CAP>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                        const __grid_constant__ CUtensorMap tmK,
@@ -174,7 +178,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                        int ring_pages, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
                        int nkv, int window, float scale_log2, int* __restrict__ error,
-                       const float* __restrict__ sink) {
+                       const float* __restrict__ sink, float cap_log2,
+                       const bf16* __restrict__ gate, int gate_stride) {
   extern __shared__ __align__(1024) uint8_t at_smem[];
   const uint32_t raw = smem_u32(at_smem);
   if (raw & 1023u) {  // swizzled tiles need it; never seen, but a wrong result must not follow
@@ -332,6 +337,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       tc_fence_after_sync();
       float s[MB_PAGE];
       tmem_ld64(tSj, s);
+      if (CAP) {  // before the mask: a masked score must stay at minus infinity
+#pragma unroll
+        for (int c = 0; c < MB_PAGE; ++c) s[c] = cap_log2 * tanh_of_2xlog2e(s[c] * scale_log2);
+      }
+      const float sl = CAP ? 1.0f : scale_log2;  // what a score is still to be multiplied by
       const int key0 = (page0 + j) * MB_PAGE;
       // a page that every row of the warp sees whole needs no mask (uniform over the warp)
       const bool whole = key0 + MB_PAGE - 1 <= pos - lane &&
@@ -349,7 +359,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int c = 0; c < MB_PAGE; c += 2) mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], s[c], s[c + 1]);
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl;
       // O is rescaled only when this row's maximum has grown by more than 2^8 (or appears for
       // the first time); until then the old reference stays and P may reach 2^8
       const bool grow = mx > m_ref + 8.0f || (m_ref == -INFINITY && mx > -INFINITY);
@@ -376,7 +386,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
       // P over the S just read, as the first operand of the second product: this thread's row,
       // two bfloat16 values a column, keys in order
       // (two scores a multiply-add and two a sum: the exponentials need the issue slots)
-      const unsigned long long scale2 = pack2(scale_log2, scale_log2), ref2 = pack2(-ref, -ref);
+      const unsigned long long scale2 = pack2(sl, sl), ref2 = pack2(-ref, -ref);
       unsigned long long l4[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c16 = 0; c16 < 2; ++c16) {
@@ -410,7 +420,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
     // limit)
     if (sink != nullptr)
       l += exp2f(sink[h] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.f : m_ref));
-    const float inv = 1.0f / l;
+    float inv = 1.0f / l;
+    if (gate != nullptr && row0 + row < n_new)
+      inv *= sigmoid_f32(__bfloat162float(gate[(size_t)(start + row0 + row) * gate_stride + h]));
     // A thread holds one row of O; written from there, a warp's store would touch 32 rows with
     // 16 bytes each. Q's shared memory is free now (every product is done): the warp lays its
     // 32 rows of 256 bytes there (16-byte piece p of row r at p ^ (r & 7): no bank conflicts
@@ -459,7 +471,8 @@ MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, v
                                       int ring_pages, const int* seq_start, const int* seq_past,
                                       const int* seq_slot, int B, int T, int max_new, int nh,
                                       int nkv, int hd, int window, float scale, int* error,
-                                      const float* sink, void* stream) {
+                                      const float* sink, float softcap, const void* gate,
+                                      int gate_stride, void* stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (hd != AT_HD) MB_FAIL("mb_attention_prefill_tc: heads of %d values (128 only)", hd);
   if (nkv <= 0 || nh % nkv) MB_FAIL("mb_attention_prefill_tc: %d heads on %d KV heads", nh, nkv);
@@ -472,18 +485,26 @@ MB_EXPORT int mb_attention_prefill_tc(const void* q, int q_stride, int q_cols, v
   if (!mb_make_map_bf16(&tmQ, q, T, q_cols, q_stride, AT_ROWS, "mb_attention_prefill_tc q")) return -1;
   if (!mb_make_map_bf16(&tmK, kpool, pool_rows, hd, hd, MB_PAGE, "mb_attention_prefill_tc k")) return -1;
   if (!mb_make_map_bf16(&tmV, vpool, pool_rows, hd, hd, MB_PAGE, "mb_attention_prefill_tc v")) return -1;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM);
-    if (e != cudaSuccess) MB_FAIL("mb_attention_prefill_tc: %s", cudaGetErrorString(e));
-    configured = true;
-  }
   const int tiles = (max_new + AT_ROWS - 1) / AT_ROWS;
   if (tiles > 65535) MB_FAIL("mb_attention_prefill_tc: %d new tokens in one sequence", max_new);
   dim3 grid(nh, tiles, B);
-  mb_launch(attn_prefill_tc_kernel, grid, dim3(AT_THREADS), AT_SMEM, (cudaStream_t)stream, tmQ,
-            tmK, tmV, (bf16*)out, out_stride, page_table, max_pages, ring_pages, seq_start,
-            seq_past, seq_slot, nh, nkv, window, scale * 1.4426950408889634f, error, sink);
+  const float log2e = 1.4426950408889634f;
+#define GO(CAP_, SCALE_)                                                                       \
+  {                                                                                            \
+    static bool configured = false;                                                            \
+    if (!configured) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<CAP_>,                       \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                           AT_SMEM);                                           \
+      if (e != cudaSuccess) MB_FAIL("mb_attention_prefill_tc: %s", cudaGetErrorString(e));     \
+      configured = true;                                                                       \
+    }                                                                                          \
+    mb_launch(attn_prefill_tc_kernel<CAP_>, grid, dim3(AT_THREADS), AT_SMEM,                   \
+              (cudaStream_t)stream, tmQ, tmK, tmV, (bf16*)out, out_stride, page_table,         \
+              max_pages, ring_pages, seq_start, seq_past, seq_slot, nh, nkv, window, SCALE_,   \
+              error, sink, softcap * log2e, (const bf16*)gate, gate_stride);                   \
+  }
+  if (softcap > 0.f) GO(true, 2.f * log2e * scale / softcap) else GO(false, scale * log2e)
+#undef GO
   MB_CHECK_LAUNCH("mb_attention_prefill_tc");
 }

@@ -189,6 +189,17 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
   *(uint2*)p = raw;
 }
 
+// tanh(x) for a score cap, as 1 - 2 / (1 + e^(2x)) with `x2` = 2 x log2(e): two special-function
+// instructions; the absolute error stays near 2e-7 for every x (small x included, where the
+// relative error grows), which is what a score under an exponential needs; +-inf give +-1.
+__device__ __forceinline__ float tanh_of_2xlog2e(float x2) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x2));
+  return 1.0f - __fdividef(2.0f, 1.0f + e);
+}
+// 1 / (1 + e^(-g))
+__device__ __forceinline__ float sigmoid_f32(float g) { return 1.0f / (1.0f + expf(-g)); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

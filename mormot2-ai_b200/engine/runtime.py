@@ -163,10 +163,10 @@ class Runtime:
         [nh], one more term of every softmax denominator; ``softcap`` > 0: a cap
         c tanh(s / c) on the scaled scores; ``gate``: one logit per (token, head) whose sigmoid
         multiplies the head's output."""
-        if self.fast_kernels and (not vd or vd == hd) and not softcap and gate is None:
+        if self.fast_kernels and (not vd or vd == hd):
             from ..parts import attention_fast
             if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale,
-                                  sink):
+                                  sink, softcap, gate, gate_stride):
                 return
         K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink,
                          softcap, gate, gate_stride)

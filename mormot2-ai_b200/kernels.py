@@ -882,70 +882,81 @@ def sample_filtered(logits: torch.Tensor, sampling, state_index: torch.Tensor,
 def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv, hd,
                      window: int, scale: float, splits: int, scratch: torch.Tensor,
                      error: Optional[torch.Tensor] = None,
-                     sink: Optional[torch.Tensor] = None) -> None:
+                     sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                     gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
     """Attention of single tokens (a decode step) over the paged cache on the tensor cores; the
-    pages of a sequence are dealt out over ``splits`` CTAs."""
+    pages of a sequence are dealt out over ``splits`` CTAs. ``softcap`` and ``gate`` as for
+    ``attention_simt``."""
     T = out.shape[0]
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert scratch.dtype == torch.float32 and scratch.is_contiguous()
+    assert gate is None or gate.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_decode",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-           _vp, _ll, _vp, _vp, _vp],
+           _vp, _ll, _vp, _vp, _f, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
           _ptr(step.tok_pos), T, nh, nkv, hd, window, float(scale),
-          splits, _ptr(scratch), scratch.numel(), _ptr(error), _ptr(sink), _stream(),
-          launches=2)
+          splits, _ptr(scratch), scratch.numel(), _ptr(error), _ptr(sink), float(softcap),
+          _ptr(gate), gate_stride, _stream(), launches=2)
 
 
 def attention_decode_clusters(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh,
                               nkv, hd, window: int, scale: float, splits: int,
                               error: Optional[torch.Tensor] = None,
-                              sink: Optional[torch.Tensor] = None) -> None:
+                              sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                              gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
     """``attention_decode`` with the splits of a (token, group of heads) as one thread-block
     cluster that merges through its shared memory: no scratch, one kernel; at most 8 splits."""
     T = out.shape[0]
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert gate is None or gate.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_decode_clusters",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-           _vp, _vp, _vp],
+           _vp, _vp, _f, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
           _ptr(step.tok_pos), T, nh, nkv, hd, window, float(scale), splits, _ptr(error),
-          _ptr(sink), _stream())
+          _ptr(sink), float(softcap), _ptr(gate), gate_stride, _stream())
 
 
 def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
                       hd, window: int, scale: float,
                       error: Optional[torch.Tensor] = None,
-                      sink: Optional[torch.Tensor] = None) -> None:
+                      sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                      gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
     """Causal attention of every sequence's new tokens over the paged cache on the tensor
     cores (the cache already holds their keys and values)."""
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert gate is None or gate.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_prefill",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
-           _vp, _vp, _vp],
+           _vp, _vp, _f, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.seq_start),
           _ptr(step.seq_past), _ptr(step.seq_slot), step.B, step.max_new, nh, nkv, hd, window,
-          float(scale), _ptr(error), _ptr(sink), _stream())
+          float(scale), _ptr(error), _ptr(sink), float(softcap), _ptr(gate), gate_stride,
+          _stream())
 
 
 def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
                          hd, window: int, scale: float, error: torch.Tensor,
-                         sink: Optional[torch.Tensor] = None) -> None:
+                         sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                         gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
     """The prefill attention on tcgen05 (heads of 128 values): S and O in tensor memory, Q, K
     and V tiles by TMA."""
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and q.stride(1) == 1
+    assert gate is None or gate.dtype == torch.bfloat16
     pool_rows = line.k.shape[0] * line.k.shape[1] * line.k.shape[2]
     _call("attention_tc", "mb_attention_prefill_tc",
           [_vp, _i, _i, _vp, _i, _vp, _vp, _ll, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-           _i, _i, _f, _vp, _vp, _vp],
+           _i, _i, _f, _vp, _vp, _f, _vp, _i, _vp],
           _ptr(q), q_stride, nh * hd, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           pool_rows, _ptr(line.page_table), line.max_pages, line.ring_pages,
           _ptr(step.seq_start), _ptr(step.seq_past), _ptr(step.seq_slot), step.B, q.shape[0],
-          step.max_new, nh, nkv, hd, window, float(scale), _ptr(error), _ptr(sink), _stream())
+          step.max_new, nh, nkv, hd, window, float(scale), _ptr(error), _ptr(sink),
+          float(softcap), _ptr(gate), gate_stride, _stream())

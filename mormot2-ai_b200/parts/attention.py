@@ -59,6 +59,11 @@ class GqaAttention(Part):
         if self.unit_after and ("q_norm" in self.names or self.head_norm_eps is None):
             raise ConfigError("a unit norm after the rotation has an eps and no weights")
         self.gate_n = self.nh if "g" in self.names else 0
+        # the gates' columns stand behind q (k, v) in the projection's rows: rows of zeros after
+        # them keep those rows a multiple of 16 bytes wide, which the tensor-core kernels ask for
+        self.gate_w = self.gate_n
+        if self.gate_n and self.qw % 8 == 0 and (self.kvw + self.vw) % 8 == 0:
+            self.gate_w = (self.gate_n + 7) // 8 * 8
         self.shared_kv = bool(p.get("shared_kv", False))
 
     can_store = True      # forward(..., store=True) writes its output into x instead of adding
@@ -96,6 +101,8 @@ class GqaAttention(Part):
                 "gate per head or value rows of their own size any size up to 1024 and 256)")
         n = self.names
         wg = weights[n["g"]] if self.gate_n else None
+        if wg is not None and self.gate_w > self.gate_n:
+            wg = torch.cat([wg, wg.new_zeros((self.gate_w - self.gate_n, wg.shape[1]))], dim=0)
         if self.shared_kv:
             # queries (and the heads' gates) only: keys and values are another layer's
             wq = weights[n["q"]]
@@ -138,7 +145,7 @@ class GqaAttention(Part):
         the gates') of the fused weight."""
         if self._q_only is None:
             w = self.qkv.weight
-            self._q_only = Linear(torch.cat([w[:self.qw], w[w.shape[0] - self.gate_n:]], dim=0)
+            self._q_only = Linear(torch.cat([w[:self.qw], w[w.shape[0] - self.gate_w:]], dim=0)
                                   if self.gate_n else w[:self.qw], self.rt)
         return self._q_only
 
@@ -153,7 +160,7 @@ class GqaAttention(Part):
                               "a cache line")
         nkv = self.nkv if writes_cache else 0
         heads_width = self.qw + nkv * (self.hd + self.vd)
-        width = heads_width + self.gate_n
+        width = heads_width + self.gate_w
         eps = float(self.head_norm_eps) if self.head_norm_eps is not None else 0.0
         inv_freq, rot_dim = (self.position.frequencies() if self.position is not None
                              else (None, 0))

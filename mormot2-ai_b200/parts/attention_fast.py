@@ -45,28 +45,35 @@ def decode_many_splits(step, nh: int, nkv: int, sms: int) -> int:
     return min(sms // groups, MANY_SPLITS_MOST)
 
 
-def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale, sink=None) -> bool:
+def run(rt, q, q_stride, out, step, line, nh, nkv, hd, window, scale, sink=None,
+        softcap: float = 0.0, gate=None, gate_stride: int = 0) -> bool:
     """True if a fast kernel took the call; False: the caller uses the general kernel.
-    ``sink``: float32 [nh], one more term exp(sink[h]) in every softmax denominator."""
+    ``sink``: float32 [nh], one more term exp(sink[h]) in every softmax denominator.
+    ``softcap`` > 0: scores become softcap * tanh(score / softcap); ``gate``: bfloat16 logits,
+    head h of token t at ``gate[t * gate_stride + h]``, whose sigmoid multiplies the head's
+    output."""
     if hd not in FAST_HEAD_DIMS or q.dtype != torch.bfloat16 or q_stride % 8 or q.data_ptr() % 16:
         return False
+    if scale <= 0 or (gate is not None and gate.dtype != torch.bfloat16):
+        return False
+    more = (softcap, gate, gate_stride)
     if step.decode:
         many = decode_many_splits(step, nh, nkv, rt.sms) if window == 0 else 0
         if many > MAX_DECODE_SPLITS and step.T * nh * many * (hd + 2) <= rt.attention_scratch.numel():
             K.attention_decode(q, q_stride, out, step, line, nh, nkv, hd, window, scale, many,
-                               rt.attention_scratch, rt.error_word, sink)
+                               rt.attention_scratch, rt.error_word, sink, *more)
             return True
         splits = decode_splits(line, step.T, nh, nkv, rt.sms, window)
         K.attention_decode_clusters(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
-                                    splits, rt.error_word, sink)
+                                    splits, rt.error_word, sink, *more)
         return True
     if out.stride(0) % 8 or out.data_ptr() % 16:
         return False
     if hd == 128 and q.stride(1) == 1:
         # S and O in tensor memory, tiles by TMA (csrc/attention_tc.cu)
         K.attention_prefill_tc(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
-                               rt.error_word, sink)
+                               rt.error_word, sink, *more)
         return True
     K.attention_prefill(q, q_stride, out, step, line, nh, nkv, hd, window, scale,
-                        rt.error_word, sink)
+                        rt.error_word, sink, *more)
     return True
