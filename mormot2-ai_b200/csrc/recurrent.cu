@@ -808,6 +808,315 @@ MB_EXPORT int mb_retention_scan(const float* z, int ld, int cq, int ck, int cv, 
   MB_CHECK_LAUNCH("mb_retention_scan");
 }
 
+// ------------------------------------------------------------------ retention, chunk by chunk
+// The same recurrence for a step that brings many tokens of a sequence. The step's tokens of a
+// sequence are cut into chunks of C; with n a chunk's tokens, S0 the state before it, g the
+// head's decay and t, s counting inside the chunk:
+//   o_t = g^(t+1) S0^T q_t + sum_{s <= t} g^(t-s) (q_t . k_s) v_s
+//   S_n = g^n S0 + sum_s g^(n-1-s) k_s v_s^T
+// Three kernels. (1) Every chunk's own sum U = sum_s g^(n-1-s) k_s v_s^T, all chunks side by
+// side. (2) The walk S0(c+1) = g^n S0(c) + U(c) over a sequence's chunks, element by element;
+// it leaves S0(c) where U(c) was and the last state in the slot. (3) Every chunk's outputs,
+// side by side again: the scores' lower triangle with its decays, both sums, the head's unit
+// norm and the gate. All of it float32 on the CUDA cores (scores and state are 32-bit
+// quantities); what is gained over the walk token by token is that the chunks of one prompt
+// fill the device instead of a block per head. W: float32 [chunks][H][D][DVp], DVp = DV rounded
+// up to 4; chunk g of the step belongs to sequence b, chunk c, in the order of the sequences.
+__device__ __forceinline__ bool chunk_of(const int* __restrict__ seq_start, int B, int C, int g,
+                                         int* b_out, int* c_out) {
+  int before = 0;
+  for (int b = 0; b < B; ++b) {
+    const int nc = (seq_start[b + 1] - seq_start[b] + C - 1) / C;
+    if (g < before + nc) {
+      *b_out = b;
+      *c_out = g - before;
+      return true;
+    }
+    before += nc;
+  }
+  return false;
+}
+
+// q and k of head hd, value i, of the token whose row of z is zr, turned by its position
+__device__ __forceinline__ float2 turned_qk(const float* __restrict__ zr, int cq, int ck, int hd,
+                                            int D, int i, int rot_dim,
+                                            const float* __restrict__ inv_freq, int pos) {
+  float qv = zr[cq + hd * D + i], kv = zr[ck + hd * D + i];
+  if (i < rot_dim) {
+    const int half = rot_dim >> 1;
+    const bool lo = i < half;
+    const int f = lo ? i : i - half, other = lo ? i + half : i - half;
+    const float angle = inv_freq[f] * (float)pos;   // float32 product
+    float sn, cs;
+    sincosf(angle, &sn, &cs);
+    const float qo = zr[cq + hd * D + other], ko = zr[ck + hd * D + other];
+    qv = lo ? qv * cs - qo * sn : qv * cs + qo * sn;
+    kv = lo ? kv * cs - ko * sn : kv * cs + ko * sn;
+  }
+  return make_float2(qv, kv);
+}
+
+// acc[p][q] += a.p * b.q
+__device__ __forceinline__ void outer4(float (&acc)[4][4], const float4 a, const float4 b) {
+  acc[0][0] = fmaf(a.x, b.x, acc[0][0]); acc[0][1] = fmaf(a.x, b.y, acc[0][1]);
+  acc[0][2] = fmaf(a.x, b.z, acc[0][2]); acc[0][3] = fmaf(a.x, b.w, acc[0][3]);
+  acc[1][0] = fmaf(a.y, b.x, acc[1][0]); acc[1][1] = fmaf(a.y, b.y, acc[1][1]);
+  acc[1][2] = fmaf(a.y, b.z, acc[1][2]); acc[1][3] = fmaf(a.y, b.w, acc[1][3]);
+  acc[2][0] = fmaf(a.z, b.x, acc[2][0]); acc[2][1] = fmaf(a.z, b.y, acc[2][1]);
+  acc[2][2] = fmaf(a.z, b.z, acc[2][2]); acc[2][3] = fmaf(a.z, b.w, acc[2][3]);
+  acc[3][0] = fmaf(a.w, b.x, acc[3][0]); acc[3][1] = fmaf(a.w, b.y, acc[3][1]);
+  acc[3][2] = fmaf(a.w, b.z, acc[3][2]); acc[3][3] = fmaf(a.w, b.w, acc[3][3]);
+}
+
+template <int C>
+__global__ void __launch_bounds__(256)
+retention_chunk_sums_kernel(const float* __restrict__ z, int ld, int ck, int cv,
+                            const float* __restrict__ decay, float k_scale,
+                            const float* __restrict__ inv_freq, int rot_dim,
+                            const int* __restrict__ tok_pos, const int* __restrict__ seq_start,
+                            int B, float* __restrict__ W, int H, int D, int DV) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  extern __shared__ __align__(16) float rc_smem[];
+  __shared__ float gp[C + 1];
+  int b, c;
+  if (!chunk_of(seq_start, B, C, blockIdx.x, &b, &c)) return;
+  const int hd = blockIdx.y, Dp = (D + 3) & ~3, DVp = (DV + 3) & ~3;
+  float* ks = rc_smem;            // [C][Dp]  g^(n-1-s) k_s, turned and scaled
+  float* vs = ks + C * Dp;        // [C][DVp]
+  const int t0 = seq_start[b] + c * C, n = min(C, seq_start[b + 1] - t0);
+  const double a = (double)decay[hd];
+  for (int e = threadIdx.x; e <= C; e += blockDim.x) gp[e] = (float)pow(a, (double)e);
+  __syncthreads();
+  for (int e = threadIdx.x; e < C * Dp; e += blockDim.x) {
+    const int s = e / Dp, i = e - s * Dp;
+    float v = 0.f;
+    if (s < n && i < D)
+      v = turned_qk(z + (size_t)(t0 + s) * ld, ck, ck, hd, D, i, rot_dim, inv_freq,
+                    tok_pos[t0 + s]).y * k_scale * gp[n - 1 - s];
+    ks[e] = v;
+  }
+  for (int e = threadIdx.x; e < C * DVp; e += blockDim.x) {
+    const int s = e / DVp, j = e - s * DVp;
+    vs[e] = (s < n && j < DV) ? z[(size_t)(t0 + s) * ld + cv + hd * DV + j] : 0.f;
+  }
+  __syncthreads();
+  float* Wc = W + ((size_t)blockIdx.x * H + hd) * D * DVp;
+  const int TJ = DVp >> 2, tiles = (Dp >> 2) * TJ;
+  for (int tile = threadIdx.x; tile < tiles; tile += blockDim.x) {
+    const int ti = tile / TJ, tj = tile - ti * TJ;
+    float acc[4][4] = {};
+    for (int s = 0; s < n; ++s)
+      outer4(acc, *(const float4*)(ks + s * Dp + 4 * ti), *(const float4*)(vs + s * DVp + 4 * tj));
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+      if (4 * ti + p < D)
+        *(float4*)(Wc + (size_t)(4 * ti + p) * DVp + 4 * tj) =
+            make_float4(acc[p][0], acc[p][1], acc[p][2], acc[p][3]);
+  }
+}
+
+template <int C>
+__global__ void __launch_bounds__(256)
+retention_chunk_carry_kernel(float* __restrict__ W, const float* __restrict__ decay,
+                             float* __restrict__ state, size_t state_stride, size_t state_off,
+                             const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                             int H, int D, int DV) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  const int b = blockIdx.z, hd = blockIdx.y, DVp = (DV + 3) & ~3, TJ = DVp >> 2;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= D * TJ) return;
+  const int i = e / TJ, j = 4 * (e - i * TJ);
+  int first = 0;
+  for (int bb = 0; bb < b; ++bb) first += (seq_start[bb + 1] - seq_start[bb] + C - 1) / C;
+  const int n = seq_start[b + 1] - seq_start[b], nc = (n + C - 1) / C;
+  if (nc == 0) return;
+  float* Sg = state + (size_t)seq_slot[b] * state_stride + state_off +
+              ((size_t)hd * D + i) * DV + j;
+  float4 S = make_float4(Sg[0], j + 1 < DV ? Sg[1] : 0.f, j + 2 < DV ? Sg[2] : 0.f,
+                         j + 3 < DV ? Sg[3] : 0.f);
+  const double a = (double)decay[hd];
+  const float whole = (float)pow(a, (double)C), last = (float)pow(a, (double)(n - (nc - 1) * C));
+  const size_t pitch = (size_t)H * D * DVp;
+  float4* w = (float4*)(W + ((size_t)first * H + hd) * D * DVp + (size_t)i * DVp + j);
+  float4 u = *w;
+  for (int c = 0; c < nc; ++c) {
+    float4* here = (float4*)((float*)w + (size_t)c * pitch);
+    float4 next = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c + 1 < nc) next = *(const float4*)((const float*)w + (size_t)(c + 1) * pitch);
+    *here = S;
+    const float f = c == nc - 1 ? last : whole;
+    S = make_float4(fmaf(f, S.x, u.x), fmaf(f, S.y, u.y), fmaf(f, S.z, u.z), fmaf(f, S.w, u.w));
+    u = next;
+  }
+  Sg[0] = S.x;
+  if (j + 1 < DV) Sg[1] = S.y;
+  if (j + 2 < DV) Sg[2] = S.z;
+  if (j + 3 < DV) Sg[3] = S.w;
+}
+
+template <typename T, int C>
+__global__ void __launch_bounds__(256)
+retention_chunk_out_kernel(const float* __restrict__ z, int ld, int cq, int ck, int cv, int cg,
+                           const float* __restrict__ decay, float k_scale,
+                           const float* __restrict__ inv_freq, int rot_dim,
+                           const int* __restrict__ tok_pos, float eps,
+                           const int* __restrict__ seq_start, int B,
+                           const float* __restrict__ W, T* __restrict__ out, int H, int D,
+                           int DV) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  extern __shared__ __align__(16) float rc_smem[];
+  __shared__ float gp[C + 1];
+  constexpr int CP = C + 4;       // the pitch of rows that hold one value of every token
+  int b, c;
+  if (!chunk_of(seq_start, B, C, blockIdx.x, &b, &c)) return;
+  const int hd = blockIdx.y, DVp = (DV + 3) & ~3;
+  float* qT = rc_smem;            // [D][CP]   q_t[i] at i * CP + t
+  float* kT = qT + D * CP;        // [D][CP]
+  float* AT = kT + D * CP;        // [C][CP]   g^(t-s) q_t . k_s at s * CP + t, zero above t
+  float* vs = AT + C * CP;        // [C][DVp]
+  float* os = vs + C * DVp;       // [C][DVp]  the outputs before the head's norm
+  const int t0 = seq_start[b] + c * C, n = min(C, seq_start[b + 1] - t0);
+  const double a = (double)decay[hd];
+  for (int e = threadIdx.x; e <= C; e += blockDim.x) gp[e] = (float)pow(a, (double)e);
+  for (int e = threadIdx.x; e < C * D; e += blockDim.x) {
+    const int s = e / D, i = e - s * D;
+    float2 v = make_float2(0.f, 0.f);
+    if (s < n) {
+      v = turned_qk(z + (size_t)(t0 + s) * ld, cq, ck, hd, D, i, rot_dim, inv_freq,
+                    tok_pos[t0 + s]);
+      v.y *= k_scale;
+    }
+    qT[i * CP + s] = v.x;
+    kT[i * CP + s] = v.y;
+  }
+  for (int e = threadIdx.x; e < C * DVp; e += blockDim.x) {
+    const int s = e / DVp, j = e - s * DVp;
+    vs[e] = (s < n && j < DV) ? z[(size_t)(t0 + s) * ld + cv + hd * DV + j] : 0.f;
+  }
+  __syncthreads();
+  constexpr int TT = C / 4;
+  for (int tile = threadIdx.x; tile < TT * TT; tile += blockDim.x) {
+    const int tt = tile / TT, ts = tile - tt * TT;
+    if (ts > tt || 4 * tt >= n) continue;
+    float acc[4][4] = {};
+    for (int i = 0; i < D; ++i)
+      outer4(acc, *(const float4*)(qT + i * CP + 4 * tt), *(const float4*)(kT + i * CP + 4 * ts));
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float r[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const int far = 4 * (tt - ts) + p - q;
+        r[p] = far >= 0 ? acc[p][q] * gp[far] : 0.f;
+      }
+      *(float4*)(AT + (4 * ts + q) * CP + 4 * tt) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+  }
+  __syncthreads();
+  const float* Wc = W + ((size_t)blockIdx.x * H + hd) * D * DVp;
+  const int TJ = DVp >> 2;
+  for (int tile = threadIdx.x; tile < TT * TJ; tile += blockDim.x) {
+    const int tt = tile / TJ, tj = tile - tt * TJ;
+    if (4 * tt >= n) continue;
+    float acc[4][4] = {};
+    for (int i = 0; i < D; ++i)
+      outer4(acc, *(const float4*)(qT + i * CP + 4 * tt),
+             __ldg((const float4*)(Wc + (size_t)i * DVp + 4 * tj)));
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float f = gp[min(C, 4 * tt + p + 1)];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[p][q] *= f;
+    }
+    const int smax = min(4 * tt + 3, n - 1);
+    for (int s = 0; s <= smax; ++s)
+      outer4(acc, *(const float4*)(AT + s * CP + 4 * tt), *(const float4*)(vs + s * DVp + 4 * tj));
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+      *(float4*)(os + (4 * tt + p) * DVp + 4 * tj) =
+          make_float4(acc[p][0], acc[p][1], acc[p][2], acc[p][3]);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int t = warp; t < n; t += warps) {
+    float ss = 0.f;
+    for (int j = lane; j < DV; j += 32) ss = fmaf(os[t * DVp + j], os[t * DVp + j], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)DV + eps);
+    const float* gr = z + (size_t)(t0 + t) * ld + cg + hd * DV;
+    T* orow = out + (size_t)(t0 + t) * H * DV + hd * DV;
+    for (int j = lane; j < DV; j += 32) {
+      const float gi = gr[j];
+      orow[j] = from_f32<T>(os[t * DVp + j] * inv * (gi / (1.0f + expf(-gi))));
+    }
+  }
+}
+
+static size_t retention_chunk_smem(int C, int D, int DV) {
+  const int DVp = (DV + 3) & ~3;
+  return sizeof(float) * ((size_t)2 * D * (C + 4) + (size_t)C * (C + 4) + (size_t)2 * C * DVp);
+}
+
+// The chunk that heads of D x DV values are walked in by mb_retention_chunked: 64, 32, or 0 when
+// even 32 tokens of such a head do not fit a block's shared memory (mb_retention_scan then).
+MB_EXPORT int mb_retention_chunk(int D, int DV) {
+  if (D <= 0 || DV <= 0) return 0;
+  if (retention_chunk_smem(64, D, DV) <= 112 * 1024) return 64;    // two blocks a multiprocessor
+  if (retention_chunk_smem(32, D, DV) <= 200 * 1024) return 32;
+  return 0;
+}
+
+// As mb_retention_scan, chunk by chunk. W: float32 scratch of w_chunks * H * D * ((DV + 3) & ~3)
+// values, w_chunks at least (T + C - 1) / C + B with C = mb_retention_chunk(D, DV).
+MB_EXPORT int mb_retention_chunked(const float* z, int ld, int cq, int ck, int cv, int cg,
+                                   const float* decay, float k_scale, const float* inv_freq,
+                                   int rot_dim, const int* tok_pos, float eps, float* state,
+                                   long long state_stride, long long state_off,
+                                   const int* seq_start, const int* seq_slot, void* out,
+                                   float* W, int w_chunks, int dtype, int T_, int B, int H,
+                                   int D, int DV, void* stream) {
+  if (B <= 0 || T_ <= 0) return 0;
+  const int C = mb_retention_chunk(D, DV);
+  if (C == 0) MB_FAIL("mb_retention_chunked: heads of %d x %d values fit no chunk", D, DV);
+  if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || (rot_dim > 0 && inv_freq == nullptr))
+    MB_FAIL("mb_retention_chunked: %d of %d values rotate", rot_dim, D);
+  if (((uintptr_t)W & 15) != 0) MB_FAIL("mb_retention_chunked: scratch off a 16-byte boundary");
+  cudaStream_t s = (cudaStream_t)stream;
+  const int chunks = (T_ + C - 1) / C + B;
+  if (w_chunks < chunks)
+    MB_FAIL("mb_retention_chunked: scratch of %d chunks, %d needed", w_chunks, chunks);
+  const int Dp = (D + 3) & ~3, DVp = (DV + 3) & ~3;
+  const size_t smem1 = sizeof(float) * (size_t)C * (Dp + DVp), smem3 = retention_chunk_smem(C, D, DV);
+  const dim3 carry((D * (DVp >> 2) + 255) / 256, H, B);
+#define GO(T_t, C_)                                                                            \
+  {                                                                                            \
+    static bool configured = false;                                                            \
+    if (!configured) {                                                                         \
+      cudaFuncSetAttribute(retention_chunk_sums_kernel<C_>,                                    \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
+      cudaFuncSetAttribute(retention_chunk_out_kernel<T_t, C_>,                                \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);           \
+      configured = true;                                                                       \
+    }                                                                                          \
+    mb_launch(retention_chunk_sums_kernel<C_>, dim3(chunks, H), dim3(256), smem1, s, z, ld, ck, \
+              cv, decay, k_scale, inv_freq, rot_dim, tok_pos, seq_start, B, W, H, D, DV);      \
+    mb_launch(retention_chunk_carry_kernel<C_>, carry, dim3(256), 0, s, W, decay, state,       \
+              (size_t)state_stride, (size_t)state_off, seq_start, seq_slot, H, D, DV);         \
+    mb_launch(retention_chunk_out_kernel<T_t, C_>, dim3(chunks, H), dim3(256), smem3, s, z, ld, \
+              cq, ck, cv, cg, decay, k_scale, inv_freq, rot_dim, tok_pos, eps, seq_start, B,   \
+              (const float*)W, (T_t*)out, H, D, DV);                                           \
+  }
+  if (dtype == MB_F32) {
+    if (C == 64) GO(float, 64) else GO(float, 32)
+  } else {
+    if (C == 64) GO(__nv_bfloat16, 64) else GO(__nv_bfloat16, 32)
+  }
+#undef GO
+  MB_CHECK_LAUNCH("mb_retention_chunked");
+}
+
 // ------------------------------------------------------------------ tanh between two products
 template <typename T>
 __global__ void tanh_kernel(const float* __restrict__ in, int ld_in, T* __restrict__ out,

@@ -76,7 +76,8 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_moe_combine": "routing", "mb_stream_step": "norms", "mb_add_scaled": "norms",
             "mb_token_shift": "recurrence", "mb_wkv_scan": "recurrence",
             "mb_mlstm_scan": "recurrence", "mb_tanh": "recurrence",
-            "mb_retention_scan": "recurrence", "mb_norm_add": "norms", "mb_cast_rows": "norms",
+            "mb_retention_scan": "recurrence", "mb_retention_chunked": "recurrence",
+            "mb_norm_add": "norms", "mb_cast_rows": "norms",
             "mb_unary_act": "activation", "mb_softcap": "activation"}
 
 
@@ -511,13 +512,26 @@ def mlstm_scan(z: torch.Tensor, cols, bi, bf, cap: float, q_scale: float, normw,
           step.B, heads, dim, vdim, _stream(), launches=1 if step.B * heads >= 96 else 2)
 
 
+def retention_chunk(dim: int, vdim: int) -> int:
+    """The chunk in which ``retention_scan`` walks a long portion of heads of dim x vdim values
+    (0: such heads are only walked token by token): what mb_retention_chunk of
+    csrc/recurrent.cu computes, from what a block stages in shared memory."""
+    def need(c):
+        return 4 * (2 * dim * (c + 4) + c * (c + 4) + 2 * c * ((vdim + 3) // 4 * 4))
+    return 64 if need(64) <= 112 * 1024 else 32 if need(32) <= 200 * 1024 else 0
+
+
 def retention_scan(z: torch.Tensor, cols, decay: torch.Tensor, k_scale: float,
                    inv_freq: Optional[torch.Tensor], rot_dim: int, eps: float,
                    state: torch.Tensor, step, out: torch.Tensor, heads: int, dim: int,
-                   vdim: int) -> None:
-    """Retention, token after token (csrc/recurrent.cu). z: the fused projection [T, ld]
-    float32; ``cols`` = the first columns of q, k, v and the output gate in it; ``decay``
-    float32 [heads] on the device. The state row of a slot holds heads x dim x vdim values."""
+                   vdim: int, chunked: Optional[bool] = None) -> None:
+    """Retention (csrc/recurrent.cu). z: the fused projection [T, ld] float32; ``cols`` = the
+    first columns of q, k, v and the output gate in it; ``decay`` float32 [heads] on the
+    device. The state row of a slot holds heads x dim x vdim values. A step of at least 128
+    tokens and two or more a sequence is walked chunk by chunk (every chunk's own sum, the
+    walk over the chunks' states, every chunk's outputs: three kernels that fill the device),
+    any other token by token; ``chunked`` forces one form. The choice depends on the step's
+    shape only, so a captured launch stays valid."""
     T = out.shape[0]
     assert z.dtype == torch.float32 and z.stride(1) == 1 and len(cols) == 4
     assert decay.dtype == torch.float32 and decay.numel() == heads
@@ -527,6 +541,21 @@ def retention_scan(z: torch.Tensor, cols, decay: torch.Tensor, k_scale: float,
     _contig(out, "out")
     assert out.shape == (T, heads * vdim) and state.dtype == torch.float32
     assert state.stride(1) == 1 and state.shape[1] >= heads * dim * vdim
+    if chunked is None:
+        chunked = T >= 128 and T >= 2 * step.B
+    C = retention_chunk(dim, vdim) if chunked else 0
+    if C:
+        chunks = (T + C - 1) // C + step.B
+        W = torch.empty((chunks, heads, dim, (vdim + 3) // 4 * 4), dtype=torch.float32,
+                        device=out.device)
+        _call("recurrent", "mb_retention_chunked",
+              [_vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _i, _vp, _f, _vp, _ll, _ll, _vp, _vp, _vp,
+               _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+              _ptr(z), z.stride(0), *[int(c) for c in cols], _ptr(decay), float(k_scale),
+              _ptr(inv_freq), rot_dim, _ptr(step.tok_pos), float(eps), _ptr(state),
+              state.stride(0), 0, _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), _ptr(W),
+              chunks, code_of(out.dtype), T, step.B, heads, dim, vdim, _stream(), launches=3)
+        return
     raw = torch.empty((T, heads * vdim), dtype=torch.float32, device=out.device)   # as in wkv_scan
     _call("recurrent", "mb_retention_scan",
           [_vp, _i, _i, _i, _i, _i, _vp, _f, _vp, _i, _vp, _f, _vp, _ll, _ll, _vp, _vp, _vp, _vp,

@@ -211,6 +211,7 @@ class RetentionMixer(Part):
             raise ConfigError(f"the mixer names the position encoding \"{p['position']}\", "
                               "which the model does not define")
         self.names = {k: prefix + v for k, v in p["names"].items()}
+        self.chunked = None     # True / False: one form of the walk whatever the step's shape
         staged = 2 * self.dim + (2 + _scan_parts(self.vdim)) * self.vdim
         if _scan_smem(self.dim, self.vdim, staged) > 200 * 1024:
             raise ConfigError(f"a retention state of {self.dim} x {self.vdim} values per head is "
@@ -254,7 +255,8 @@ class RetentionMixer(Part):
                              else (None, 0))
         y = torch.empty((T, self.nh * self.vdim), dtype=self.rt.dtype, device=h.device)
         K.retention_scan(z, self.cols, self.decay_dev, self.dim ** -0.5, inv_freq, rot_dim,
-                         self.eps, state, step, y, self.nh, self.dim, self.vdim)
+                         self.eps, state, step, y, self.nh, self.dim, self.vdim,
+                         chunked=self.chunked)
         return _project(self.o, y, x, store)
 
 

@@ -258,6 +258,45 @@ def test_retention_alone(dtype, heads, dim, vdim, hidden, rot):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,dim,vdim,hidden,rot", [
+    (3, 20, 12, 40, {"base": 500.0, "dims": 20}), (1, 9, 22, 50, None),
+    (2, 64, 128, 64, {"base": 1e4, "dims": 64}), (2, 128, 64, 64, {"base": 1e4, "dims": 32}),
+    (1, 64, 200, 48, {"base": 1e4, "dims": 2}), (1, 128, 160, 32, {"base": 3e3, "dims": 64})])
+def test_retention_chunk_by_chunk(dtype, heads, dim, vdim, hidden, rot):
+    """The walk chunk by chunk (what a long portion takes) and the walk token by token give the
+    plain outputs and leave the plain state: sequences that end inside a chunk, one token
+    behind a chunk's last, and a single token, in one step; then portions that take turns
+    between the two forms, so that either starts from the state the other left."""
+    rt = Runtime(TORCH[dtype])
+    decay = [0.97, 1.0, 0.5][:heads]
+    mixer = retention_of(hidden, heads, dim, vdim, decay, rot, rt)
+    assert K.retention_chunk(dim, vdim) in (32, 64)
+    w, ref = part_weights(mixer, seed=dim + 1)
+    mixer.bind(to_dev(w, dtype), rt)
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "rot": rot}
+    rng = np.random.default_rng(vdim)
+    hs = [rounded(rng.normal(0, 1, (n, hidden)), dtype) for n in (193, 65, 1, 150)]
+    plain_runs = [plain.retention_mixer(h, ref, "m.", m, 1e-5, np.arange(len(h))) for h in hs]
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    for form, cuts in ((True, [(0, 200)]), (False, [(0, 200)]),
+                       (True, [(0, 3), (3, 67), (67, 131), (131, 200)]),
+                       (None, [(0, 130), (130, 132), (132, 200)])):
+        mixer.chunked = form
+        state = torch.zeros((4,) + mixer.state_need().shape, device=DEV)
+        got = run_mixer(mixer, hs, cuts, hidden, dtype, state=state, store=True)
+        for g, (want, _) in zip(got, plain_runs):
+            check(g, want, dtype, f"chunked {form}, cuts {cuts}")
+        for slot, (_, S) in zip([2, 0, 1, 3], plain_runs):
+            have = state[slot].cpu().double().numpy().reshape(S.shape)
+            assert np.abs(have - S).max() <= tol * max(1.0, np.abs(S).max()), (form, slot)
+
+
+def test_retention_heads_too_large_for_a_chunk_are_walked_token_by_token():
+    assert K.retention_chunk(512, 512) == 0 and K.retention_chunk(64, 64) == 64
+    assert K.retention_chunk(64, 128) == 32
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far", [2, 63, 64, 500])
 def test_retention_keeps_a_token_from_far_back(dtype, far):
     """With a decay of one the first token's key is made the one that the last query meets
@@ -284,10 +323,12 @@ def test_retention_keeps_a_token_from_far_back(dtype, far):
     h[-2, 0] = 1.0 / 64                          # a near token that is faintly along e_0 too
     m = {"heads": heads, "dim": dim, "vdim": vdim, "decay": [1.0, d]}
     want = plain.retention_mixer(h, W, "m.", m, 1e-5, np.arange(n))[0]
-    state = torch.zeros((4,) + mixer.state_need().shape, device=DEV)
     cuts = [(0, n)] if far < 500 else [(0, 300), (300, n - 1), (n - 1, n)]
-    got = run_mixer(mixer, [h], cuts, hidden, dtype, state=state, store=True)[0]
-    check(got[-1:], want[-1:], dtype, f"a token {far} back")
+    for form in (None, True, False):             # as the step's shape chooses, then either form
+        mixer.chunked = form
+        state = torch.zeros((4,) + mixer.state_need().shape, device=DEV)
+        got = run_mixer(mixer, [h], cuts, hidden, dtype, state=state, store=True)[0]
+        check(got[-1:], want[-1:], dtype, f"a token {far} back, chunked {form}")
     # head 0 in closed form: the far token, the faint near one and the last token itself
     gate = plain.silu(h[-1] @ W["m.mix.g"].T)
     Wv = W["m.mix.v"][:vdim]
