@@ -78,6 +78,21 @@ __device__ __forceinline__ float gated_mul(float g, float u, int mode) {
   }
   return silu_mul(g, u);
 }
+// An activation of the stored product itself (mode TC_STORE, K not split), in bits 8 and up of
+// the mode that a kernel is given: 1 SiLU, 2 the tanh form of GELU, 4 the square of relu.
+__device__ __forceinline__ void unary16(float* v, int act) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float x = v[j];
+    if (act == 4) {
+      const float r = fmaxf(x, 0.f);
+      v[j] = r * r;
+    } else {
+      const float z = act == 2 ? 1.5957691216057308f * (x + 0.044715f * x * x * x) : x;
+      v[j] = __fdividef(x, 1.0f + __expf(-z));
+    }
+  }
+}
 __device__ __forceinline__ float pair_bias(const float* part, int row) {
   return part ? __bfloat162float(((const __nv_bfloat16*)part)[row]) : 0.f;
 }
@@ -147,7 +162,7 @@ __device__ __forceinline__ void store_row16(const float* v, void* C, int c_dtype
 __device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, int lane, int row0,
                                             int n0, int width, int M, int N, void* C, int c_dtype,
                                             long long ldc, int mode, float* part,
-                                            long long partial_ld) {
+                                            long long partial_ld, int act) {
   const int acc_cols = mode >= TC_SWIGLU ? 128 : (c_dtype == MB_BF16 && mode == TC_STORE ? 64 : 32);
   const uint32_t mine = stage_w + lane * 128;
 #pragma unroll 1
@@ -158,6 +173,7 @@ __device__ __forceinline__ void staged_rows(uint32_t taddr, uint32_t stage_w, in
     for (int g = 0; g * 16 < ncols; ++g) {
       float v[16];
       tmem_ld16(taddr + c0 + 16 * g, v);
+      if (act) unary16(v, act);
       if (mode >= TC_SWIGLU) {
         if (part) {
 #pragma unroll
@@ -235,10 +251,11 @@ template <int BN, bool SWAP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                void* __restrict__ C, int c_dtype, long long ldc, int rowsA, int rowsB, int K,
-               int kb_per_split, int mode, float* __restrict__ partial, long long partial_stride,
+               int kb_per_split, int mode_act, float* __restrict__ partial, long long partial_stride,
                long long partial_ld, int tile_rows, int stages, int a_stage, int tiles_a,
                int tiles_b, int num_tiles, int* __restrict__ error) {
   using Cfg = TcCfg<BN>;
+  const int mode = mode_act & 255, act = mode_act >> 8;
   MB_TRACE_BEGIN();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -375,7 +392,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       float* part = partial ? partial + z * partial_stride : nullptr;
       if (staged) {
         staged_rows(taddr, stage_w, lane, a - lane, n0, BN, rowsA, rowsB, C, c_dtype, ldc, mode,
-                    part, partial_ld);
+                    part, partial_ld, act);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty0 + 8 * b);
@@ -386,6 +403,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (n0 + c0 >= rowsB) break;  // uniform over the warp
         float v[16];
         tmem_ld16(taddr + c0, v);
+        if (act) unary16(v, act);
         if (SWAP && mode >= TC_SWIGLU) {
           // lanes 2i and 2i+1 hold gate and up of output feature (m0 + lane_row) / 2
           const float bias = mine ? pair_bias(part, a) : 0.f;
@@ -452,9 +470,10 @@ template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     void* __restrict__ C, int c_dtype, long long ldc, int M, int N, int K,
-                    int kb_per_split, int mode, float* __restrict__ partial,
+                    int kb_per_split, int mode_act, float* __restrict__ partial,
                     long long partial_stride, long long partial_ld, int tiles_m, int tiles_n,
                     int num_tiles, int* __restrict__ error) {
+  const int mode = mode_act & 255, act = mode_act >> 8;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -565,13 +584,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       float* part = partial ? partial + z * partial_stride : nullptr;
       if (staged) {
         staged_rows(taddr, stage_w, lane, a - lane, n0, BN, M, N, C, c_dtype, ldc, mode, part,
-                    partial_ld);
+                    partial_ld, act);
       } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (n0 + c0 >= N) break;
         float v[16];
         tmem_ld16(taddr + c0, v);
+        if (act) unary16(v, act);
         if (a < M)
           store_row16(v, C, c_dtype, ldc, a, n0 + c0, N, mode, part, partial_ld, partial_stride);
       }
@@ -744,8 +764,8 @@ MB_EXPORT int mb_gemm_tc_supported(const void* A, int lda, const void* W, int M,
 }
 
 // C[M, N] (row stride ldc; bfloat16 or float32) = A[M, K] (row stride lda) · W[N, K]ᵀ
-// (epilogue 0), C += ... (1, float32 C), or C[M, N / 2] = SwiGLU over a W whose rows alternate
-// gate and up (3, bfloat16 C). `workspace` (float32, may be null) lets the K range be split;
+// (epilogue 0; with an activation in bits 8 and up, C = act(A · Wᵀ)), C += ... (1, float32 C), or
+// C[M, N / 2] = SwiGLU over a W whose rows alternate gate and up (3, bfloat16 C). `workspace` (float32, may be null) lets the K range be split;
 // `error` is a device word that receives a non-zero code if a wait in the kernel ran out
 // (1 load, 2 MMA, 3 epilogue). `sms`: the number of SMs of the device. `defer`: when K was split
 // (mb_gemm_tc_last_splits() > 1) the partial sums stay in the workspace as [splits][M][N] and C
@@ -760,6 +780,13 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
   g_last_splits = 1;
   if (M <= 0 || N <= 0) return 0;
   if (!mb_gemm_tc_supported(A, lda, W, M, N, K)) return -1;
+  // bits 8 and up: an activation of the stored product (1 SiLU, 2 GELU's tanh form, 4 relu
+  // squared); K is then not split, since the sums must be whole before it
+  const int act = epilogue >> 8;
+  epilogue &= 255;
+  if (act != 0 && (epilogue != TC_STORE || (act != 1 && act != 2 && act != 4)))
+    MB_FAIL("mb_gemm_tc: activation %d with epilogue %d", act, epilogue);
+  if (act) workspace = nullptr;
   if (epilogue != TC_STORE && epilogue != TC_ADD && epilogue != TC_SWIGLU && epilogue != TC_GEGLU)
     MB_FAIL("mb_gemm_tc: epilogue %d", epilogue);
   if (epilogue == TC_ADD && c_dtype != MB_F32) MB_FAIL("mb_gemm_tc: the residual is float32");
@@ -838,7 +865,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     CUtensorMap tmA, tmB;
     if (!mb_make_map_bf16(&tmA, A, M, K, lda, 128, "mb_gemm_tc input")) return -1;
     if (!mb_make_map_bf16(&tmB, W, N, K, K, bn / 2, "mb_gemm_tc weight")) return -1;
-    const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
+    const int mode = p.splits > 1 ? TC_PARTIAL : (epilogue | (act << 8));
     float* partial = p.splits > 1 ? workspace : (float*)g_pair_bias;
     int rc = 0;
     switch (bn) {
@@ -872,7 +899,7 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     if (!mb_make_map_bf16(&tmA, A, M, K, lda, TC_BM, "mb_gemm_tc input")) return -1;
     if (!mb_make_map_bf16(&tmB, W, N, K, K, bn, "mb_gemm_tc weight")) return -1;
   }
-  const int mode = p.splits > 1 ? TC_PARTIAL : epilogue;
+  const int mode = p.splits > 1 ? TC_PARTIAL : (epilogue | (act << 8));
   float* partial = p.splits > 1 ? workspace : (float*)g_pair_bias;
   const long long pstride = (long long)M * N, pld = N;
   int rc;

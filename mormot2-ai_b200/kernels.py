@@ -837,9 +837,10 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
             workspace: Optional[torch.Tensor], error: torch.Tensor, sms: int,
-            swiglu: bool = False, defer: bool = False) -> int:
+            swiglu: bool = False, defer: bool = False, act: Optional[int] = None) -> int:
     """c = a · wᵀ (or c += for a float32 c) with bfloat16 a [M, K] and w [N, K] on the tensor
     cores; ``swiglu``: w's rows alternate gate and up and c [M, N / 2] = silu(gate) · up.
+    ``act`` (ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED): c = act(a · wᵀ), in the epilogue.
     ``workspace``: float32 scratch for split sums; ``error``: int32 device word. ``defer``:
     when K was split (the return value, the number of splits, is above 1) the partial sums stay
     in the workspace as [splits, M, N] and c is not touched."""
@@ -848,10 +849,14 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, add: bool,
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
     assert a.stride(1) == 1 and c.stride(1) == 1 and c.shape == (M, N // 2 if swiglu else N)
     _contig(w, "the weight")
+    epilogue = 3 if swiglu else (1 if add else 0)
+    if act is not None:
+        assert epilogue == 0 and act in (ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED)
+        epilogue |= (act + 1) << 8
     _call("gemm_tc", "mb_gemm_tc",
           [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _ll, _i, _vp, _i, _vp],
           _ptr(a), a.stride(0), _ptr(w), _ptr(c), code_of(c.dtype), c.stride(0), M, N, K,
-          3 if swiglu else (1 if add else 0), _ptr(workspace),
+          epilogue, _ptr(workspace),
           workspace.numel() if workspace is not None else 0, 1 if defer else 0,
           _ptr(error), sms, _stream())
     # the split of K adds one kernel that sums the partial products

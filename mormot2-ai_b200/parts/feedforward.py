@@ -162,16 +162,14 @@ class PlainMlp(Part):
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.rt = rt
-        self.up = Linear(weights[self.names["up"]], rt)
+        self.up = Linear(weights[self.names["up"]], rt, unary=self.act)
         self.down = Linear(weights[self.names["down"]], rt)
 
     def forward(self, h, x, step, store: bool = False):
         """Adds the feed-forward's output into x (``store``: writes it there), or returns it as
         ``Pending`` split sums for whoever reads it next (x is then not touched)."""
         from .linear import Pending
-        z = self.up(h)
-        act = torch.empty_like(z)
-        K.unary_act(z, act, self.act)
+        act = self.up(h)          # the activation in the product's epilogue
         if store:
             out = self.down(act, out=x, defer=True)
         else:

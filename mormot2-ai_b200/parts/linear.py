@@ -27,17 +27,22 @@ class Pending:
 
 class Linear:
     def __init__(self, weight: torch.Tensor, rt, swiglu: bool = False, activation: int = 0,
-                 pair_bias: Optional[torch.Tensor] = None):
+                 pair_bias: Optional[torch.Tensor] = None, unary: Optional[int] = None):
         """``swiglu``: the weight is [2 * out, in] with rows that alternate gate and up (row 2i
         the gate, row 2i + 1 the up projection of output i) and the product is followed by
         out = silu(gate) * up in the kernel's epilogue. ``activation`` (``kernels.ACT_*``)
         other than SiLU, or ``pair_bias`` ([2 * out], alternating like the rows, added before
-        the activation): only the tensor-core kernel has that epilogue."""
+        the activation): only the tensor-core kernel has that epilogue. ``unary``
+        (``kernels.ACT_*``): the stored product is act(a · Wᵀ), in the tensor-core kernel's
+        epilogue or by a kernel after the exact product; such a product is never added into a
+        residual or left as split sums."""
         self.weight = weight.contiguous()
         self.rt = rt
         self.swiglu = swiglu
         self.activation, self.pair_bias = activation, pair_bias
         self.plain_swiglu = activation == K.ACT_SILU and pair_bias is None
+        self.unary = unary
+        assert unary is None or not swiglu
         self.out_features = weight.shape[0] // (2 if swiglu else 1)
         self.in_features = weight.shape[1]
         self.fast = None
@@ -46,6 +51,8 @@ class Linear:
             self.fast = FastLinear.maybe(self.weight, rt, swiglu)
             if self.fast is not None and swiglu and not self.plain_swiglu:
                 self.fast.gated = (activation, pair_bias)
+            if self.fast is not None:
+                self.fast.unary = unary
 
     def __call__(self, a: torch.Tensor, out: Optional[torch.Tensor] = None,
                  add_into: Optional[torch.Tensor] = None,
@@ -55,6 +62,7 @@ class Linear:
         the kernel splits K, a ``Pending`` with the partial sums is returned instead and neither
         ``out`` nor ``add_into`` is touched."""
         M = a.shape[0]
+        assert self.unary is None or (add_into is None and not defer)
         if self.fast is not None and defer and not self.swiglu:
             pending = self.fast.deferred(a)
             if pending is not None:
@@ -71,5 +79,10 @@ class Linear:
         if add_into is not None:
             K.gemm_simt(a, self.weight, add_into, K.EPI_ADD)
             return add_into
+        if self.unary is not None:
+            z = torch.empty_like(out)
+            K.gemm_simt(a, self.weight, z, K.EPI_STORE)
+            K.unary_act(z, out, self.unary)
+            return out
         K.gemm_simt(a, self.weight, out, K.EPI_SWIGLU_PAIRS if self.swiglu else K.EPI_STORE)
         return out

@@ -15,6 +15,7 @@ from .. import kernels as K
 class FastLinear:
     def __init__(self, weight: torch.Tensor, rt, swiglu: bool):
         self.weight, self.rt, self.swiglu = weight, rt, swiglu
+        self.unary = None       # an activation of the stored product, in the epilogue
         self.gated = None       # (activation, pair bias) of a gated epilogue that is not plain SwiGLU
 
     @classmethod
@@ -55,6 +56,8 @@ class FastLinear:
             return True
         if add_into is not None:
             K.gemm_tc(a, self.weight, add_into, True, rt.workspace, rt.error_word, rt.sms)
+        elif self.unary is not None:
+            K.gemm_tc(a, self.weight, out, False, None, rt.error_word, rt.sms, act=self.unary)
         else:
             K.gemm_tc(a, self.weight, out, False, rt.workspace, rt.error_word, rt.sms)
         return True

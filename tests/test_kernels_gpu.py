@@ -161,6 +161,15 @@ def test_gemm_tensor_cores(rt, M, N, Kd):
         K.gemm_tc(a.to(DEV), w.to(DEV), c, False, rt.workspace, rt.error_word, rt.sms, swiglu=True)
         y = want.float().numpy()
         assert rel(c.float().cpu(), plain.swiglu(y[:, 0::2], y[:, 1::2])) <= 8e-3
+    # an activation of the stored product (the scratch is given: K must not be split all the same)
+    y = want
+    forms = {K.ACT_RELU_SQUARED: torch.clamp(y, min=0) ** 2, K.ACT_SILU: y * torch.sigmoid(y),
+             K.ACT_GELU_TANH: 0.5 * y * (1 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))}
+    for act, wanted in forms.items():
+        for c_dt, tol in ((torch.bfloat16, 8e-3), (torch.float32, 3e-5)):
+            c = torch.full((M, N), 3.0, dtype=c_dt, device=DEV)
+            K.gemm_tc(a.to(DEV), w.to(DEV), c, False, rt.workspace, rt.error_word, rt.sms, act=act)
+            assert rel(c.float().cpu(), wanted) <= tol, (act, c_dt)
     rt.check()
 
 
