@@ -836,6 +836,10 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     const int tiles = ((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
     if (workspace && epilogue < TC_SWIGLU && tiles < sms && nkb >= 8) {
       int want = (2 * sms + tiles - 1) / tiles;
+      // sums that stay pending are read once more by their consumer, a full pass over the
+      // output per split: then only as many splits as fill the device once
+      if (defer && want > sms / tiles) want = sms / tiles;
+      if (defer && want > TC_MAX_SPLITS) want = TC_MAX_SPLITS;
       if (want > nkb / 4) want = nkb / 4;
       const long long per = (long long)M * N;
       if (want > workspace_floats / per) want = (int)(workspace_floats / per);
@@ -855,6 +859,8 @@ MB_EXPORT int mb_gemm_tc(const void* A, int lda, const void* W, void* C, int c_d
     p.splits = 1;
     if (workspace && epilogue < TC_SWIGLU && tiles < pairs && nkb >= 8) {
       int want = (2 * pairs + tiles - 1) / tiles;
+      if (defer && want > pairs / tiles) want = pairs / tiles;   // as above
+      if (defer && want > TC_MAX_SPLITS) want = TC_MAX_SPLITS;
       if (want > nkb / 4) want = nkb / 4;
       const long long per = (long long)M * N;
       if (want > workspace_floats / per) want = (int)(workspace_floats / per);

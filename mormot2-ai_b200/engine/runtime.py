@@ -38,8 +38,9 @@ class Runtime:
                                 self.device, None) if self.fast_kernels else None)
         # the partial sums of a split product that its consumer adds up (parts/linear.py): two
         # halves used in turn, so that two products may be pending at once (a block with two
-        # branches that both defer their sums)
-        self.pending_bufs = ([alloc(guards, f"pending split sums {i}", (4 << 20,), torch.float32,
+        # branches that both defer their sums); 128 MB each: a prefill's output products of
+        # 8,192 tokens x 4,096 columns still split once
+        self.pending_bufs = ([alloc(guards, f"pending split sums {i}", (32 << 20,), torch.float32,
                                     self.device, None) for i in range(2)]
                              if self.fast_kernels else None)
         self.pending_turn = 0

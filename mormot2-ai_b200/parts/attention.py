@@ -202,7 +202,7 @@ class GqaAttention(Part):
     def _project(self, attn, x, store: bool):
         from .linear import Pending
         if store:       # stored into x, or left pending (x is then not touched)
-            out = self.o(attn, out=x, defer=True)
+            out = self.o(attn, out=x, defer="any")
             return out if isinstance(out, Pending) else None
         out = self.o(attn, add_into=x, defer=True)
         return out if isinstance(out, Pending) else None

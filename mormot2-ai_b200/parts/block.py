@@ -271,7 +271,7 @@ class OutputNormResidualBlock(Part):
             g = torch.empty_like(z)
             K.unary_act(z, g, self.side_act, self.side_table, int(sd["col0"]), step.tok_ids)
             from .linear import Pending
-            t = self.side_proj(g, out_dtype=torch.float32, defer=True)
+            t = self.side_proj(g, out_dtype=torch.float32, defer="any")
             h_next = self._next_operand(x)
             K.norm_add(t.partial if isinstance(t, Pending) else t, self.side_norm,
                        float(sd["eps"]), x, h_next)

@@ -171,7 +171,7 @@ class PlainMlp(Part):
         from .linear import Pending
         act = self.up(h)          # the activation in the product's epilogue
         if store:
-            out = self.down(act, out=x, defer=True)
+            out = self.down(act, out=x, defer="any")
         else:
             out = self.down(act, add_into=x, defer=True)
         return out if isinstance(out, Pending) else None

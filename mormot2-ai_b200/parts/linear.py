@@ -60,11 +60,12 @@ class Linear:
         """``add_into``: the float32 residual [M, out] that the product is added to (returned).
         Otherwise the product (or its SwiGLU) is stored in ``out`` (made if None). ``defer``: if
         the kernel splits K, a ``Pending`` with the partial sums is returned instead and neither
-        ``out`` nor ``add_into`` is touched."""
+        ``out`` nor ``add_into`` is touched; ``defer="any"`` asks for that also in a step of many
+        tokens (the caller's next kernel adds up to 8 sums a row), True only in one of few."""
         M = a.shape[0]
         assert self.unary is None or (add_into is None and not defer)
         if self.fast is not None and defer and not self.swiglu:
-            pending = self.fast.deferred(a)
+            pending = self.fast.deferred(a, any_rows=defer == "any")
             if pending is not None:
                 return pending
         if add_into is None and out is None:

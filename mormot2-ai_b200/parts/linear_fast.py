@@ -24,13 +24,14 @@ class FastLinear:
             return None
         return cls(weight, rt, swiglu)
 
-    def deferred(self, a: torch.Tensor):
+    def deferred(self, a: torch.Tensor, any_rows: bool = False):
         """The product with its split sums left pending, or None if this call does not split
-        (few tokens and a weight with few row tiles split; see csrc/gemm_tc.cu)."""
+        (few tokens and a weight with few row tiles split; see csrc/gemm_tc.cu). ``any_rows``:
+        also a step of many tokens, whose consumer then adds up to 8 sums a row."""
         from .linear import Pending
         rt = self.rt
         M, N = a.shape[0], self.weight.shape[0]
-        if (a.dtype != torch.bfloat16 or a.stride(0) % 8 or a.data_ptr() % 16 or M > 64
+        if (a.dtype != torch.bfloat16 or a.stride(0) % 8 or a.data_ptr() % 16 or (M > 64 and not any_rows)
                 or -(-N // 128) > rt.sms or rt.pending_bufs is None):
             return None
         # c is only written when the kernel does not split after all

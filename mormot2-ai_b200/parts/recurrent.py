@@ -57,7 +57,7 @@ def _project(linear: Linear, y, x, store: bool):
     of a step of few tokens splits its sums, left as ``Pending`` for whoever reads it next (x is
     then not touched)."""
     if store:
-        out = linear(y, out=x, defer=True)
+        out = linear(y, out=x, defer="any")
         return out if isinstance(out, Pending) else None
     linear(y, add_into=x)
     return None
