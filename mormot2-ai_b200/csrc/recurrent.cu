@@ -939,16 +939,24 @@ retention_chunk_carry_kernel(float* __restrict__ W, const float* __restrict__ de
   const double a = (double)decay[hd];
   const float whole = (float)pow(a, (double)C), last = (float)pow(a, (double)(n - (nc - 1) * C));
   const size_t pitch = (size_t)H * D * DVp;
-  float4* w = (float4*)(W + ((size_t)first * H + hd) * D * DVp + (size_t)i * DVp + j);
-  float4 u = *w;
-  for (int c = 0; c < nc; ++c) {
-    float4* here = (float4*)((float*)w + (size_t)c * pitch);
-    float4 next = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c + 1 < nc) next = *(const float4*)((const float*)w + (size_t)(c + 1) * pitch);
-    *here = S;
-    const float f = c == nc - 1 ? last : whole;
-    S = make_float4(fmaf(f, S.x, u.x), fmaf(f, S.y, u.y), fmaf(f, S.z, u.z), fmaf(f, S.w, u.w));
-    u = next;
+  float* w = W + ((size_t)first * H + hd) * D * DVp + (size_t)i * DVp + j;
+  // the chunks' sums do not depend on the state: eight loads in flight, then eight steps
+  constexpr int AHEAD = 8;
+  for (int c0 = 0; c0 < nc; c0 += AHEAD) {
+    float4 u[AHEAD];
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k)
+      u[k] = c0 + k < nc ? *(const float4*)(w + (size_t)(c0 + k) * pitch)
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < AHEAD; ++k) {
+      if (c0 + k < nc) {
+        *(float4*)(w + (size_t)(c0 + k) * pitch) = S;
+        const float f = c0 + k == nc - 1 ? last : whole;
+        S = make_float4(fmaf(f, S.x, u[k].x), fmaf(f, S.y, u[k].y), fmaf(f, S.z, u[k].z),
+                        fmaf(f, S.w, u[k].w));
+      }
+    }
   }
   Sg[0] = S.x;
   if (j + 1 < DV) Sg[1] = S.y;
