@@ -15,6 +15,8 @@
 //                 o = S^T q / (max(|n.q|, e^(-m')) + 1e-6); then o / rms(o) * norm * sigmoid(g)
 //   retention_scan  q, k turned by the position; S <- decay S + (k / sqrt(D)) v^T; o = S^T q;
 //                 then o / rms(o) * silu(g)
+//   retention_chunked  the same recurrence chunk by chunk (three kernels) for a step that
+//                 brings many tokens of a sequence
 #include "common.cuh"
 
 MB_DEFINE_LAST_ERROR
