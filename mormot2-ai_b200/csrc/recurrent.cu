@@ -772,11 +772,17 @@ MB_EXPORT int mb_retention_scan(const float* z, int ld, int cq, int ck, int cv, 
     MB_FAIL("mb_retention_scan: heads of %d x %d values (at most 512 each)", D, DV);
   if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || (rot_dim > 0 && inv_freq == nullptr))
     MB_FAIL("mb_retention_scan: %d of %d values rotate", rot_dim, D);
-  const int NS = raw ? scan_slices(B, H, D, DV, 32) : 1;
-  const int CW = (DV + NS - 1) / NS;
-  const int P = scan_parts(CW), per = (D + P - 1) / P;
-  const int R = per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : 0;
-  const size_t smem = retention_smem_bytes(D, CW, P, R);
+  int NS = raw ? scan_slices(B, H, D, DV, 32) : 1, CW, P, R;
+  size_t smem;
+  for (;; NS *= 2) {
+    CW = (DV + NS - 1) / NS;
+    P = scan_parts(CW);
+    const int per = (D + P - 1) / P;
+    R = per <= 8 ? 8 : per <= 16 ? 16 : per <= 32 ? 32 : 0;
+    smem = retention_smem_bytes(D, CW, P, R);
+    // a head whose state does not fit one block's shared memory: narrower slices of its columns
+    if (smem <= 200 * 1024 || !raw || CW <= 32) break;
+  }
   if (smem > 200 * 1024)
     MB_FAIL("mb_retention_scan: heads of %d x %d values (what a block stages must fit 200 KB)",
             D, DV);

@@ -52,6 +52,25 @@ def _scan_smem(dim: int, vdim: int, staged_per_token: int) -> int:
     return 4 * (state + 16 * staged_per_token + 256)
 
 
+def _retention_fits(dim: int, vdim: int) -> bool:
+    """Whether the walk token by token has a slice of a head's value columns (all of them, a
+    half, a quarter, ... down to 32) whose block fits 200 KB of shared memory: what
+    mb_retention_scan of csrc/recurrent.cu looks for."""
+    if not (0 < dim <= 512 and 0 < vdim <= 512):
+        return False
+    ns = 1
+    while True:
+        cw = -(-vdim // ns)
+        parts = _scan_parts(cw)
+        rows = -(-dim // parts)
+        state = 0 if rows <= 32 else (dim * cw + 3) // 4 * 4
+        if 4 * (state + 16 * (2 * dim + (2 + parts) * cw) + 128) <= 200 * 1024:
+            return True
+        if cw <= 32:
+            return False
+        ns *= 2
+
+
 def _project(linear: Linear, y, x, store: bool):
     """The output product: added into x, or (``store``) written into x, or, where the product
     of a step of few tokens splits its sums, left as ``Pending`` for whoever reads it next (x is
@@ -212,8 +231,7 @@ class RetentionMixer(Part):
                               "which the model does not define")
         self.names = {k: prefix + v for k, v in p["names"].items()}
         self.chunked = None     # True / False: one form of the walk whatever the step's shape
-        staged = 2 * self.dim + (2 + _scan_parts(self.vdim)) * self.vdim
-        if _scan_smem(self.dim, self.vdim, staged) > 200 * 1024:
+        if not _retention_fits(self.dim, self.vdim):
             raise ConfigError(f"a retention state of {self.dim} x {self.vdim} values per head is "
                               "more than the kernel keeps on one multiprocessor")
 

@@ -229,7 +229,8 @@ def retention_of(hidden, heads, dim, vdim, decay, rot, rt):
 @pytest.mark.parametrize("heads,dim,vdim,hidden,rot", [
     (3, 20, 12, 40, {"base": 500.0, "dims": 20}), (2, 32, 48, 96, {"base": 2e5, "dims": 32}),
     (1, 9, 22, 50, None), (2, 128, 64, 64, {"base": 1e4, "dims": 32}),
-    (1, 64, 200, 48, {"base": 1e4, "dims": 2}), (5, 6, 6, 30, {"base": 77.0, "dims": 4})])
+    (1, 64, 200, 48, {"base": 1e4, "dims": 2}), (5, 6, 6, 30, {"base": 77.0, "dims": 4}),
+    (1, 256, 256, 24, {"base": 1e4, "dims": 256}), (1, 512, 320, 16, None)])
 def test_retention_alone(dtype, heads, dim, vdim, hidden, rot):
     """Whole sequences, then the same in portions of 1, 2 and 30 tokens with a batch mate: the
     state carries over and slots' states do not mix. Decays from fast to exactly one."""
@@ -261,7 +262,8 @@ def test_retention_alone(dtype, heads, dim, vdim, hidden, rot):
 @pytest.mark.parametrize("heads,dim,vdim,hidden,rot", [
     (3, 20, 12, 40, {"base": 500.0, "dims": 20}), (1, 9, 22, 50, None),
     (2, 64, 128, 64, {"base": 1e4, "dims": 64}), (2, 128, 64, 64, {"base": 1e4, "dims": 32}),
-    (1, 64, 200, 48, {"base": 1e4, "dims": 2}), (1, 128, 160, 32, {"base": 3e3, "dims": 64})])
+    (1, 64, 200, 48, {"base": 1e4, "dims": 2}), (1, 128, 160, 32, {"base": 3e3, "dims": 64}),
+    (1, 256, 256, 24, {"base": 1e4, "dims": 256})])
 def test_retention_chunk_by_chunk(dtype, heads, dim, vdim, hidden, rot):
     """The walk chunk by chunk (what a long portion takes) and the walk token by token give the
     plain outputs and leave the plain state: sequences that end inside a chunk, one token
