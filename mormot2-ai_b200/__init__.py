@@ -4,7 +4,7 @@ Qwen3 dense decoder: everything between a request's token ids and its next token
     from mormot2_ai_b200 import Engine, Entry, Qwen3Config, write_random_model
 """
 from . import parts  # registers the built-in parts
-from .config import (ModelSpec, PartSpec, Qwen3Config, BusavikConfig, FimudraConfig, SezopelConfig, Run, LayerSpec, architectures,
+from .config import (ModelSpec, PartSpec, Qwen3Config, BusavikConfig, FimudraConfig, SezopelConfig, LaralixConfig, Run, LayerSpec, architectures,
                      config_of_folder, register_architecture)
 from .errors import CacheError, ConfigError, InferError, KernelError, WeightsError
 from .weights import SafeTensorsFolder, write_random_model, write_safetensors
@@ -12,7 +12,7 @@ from .engine import DecoderModel, Engine, Entry, Runtime
 from .sampling import Sampling, sampling_from_config
 from .client import LlmClient
 
-__all__ = ["ModelSpec", "PartSpec", "Qwen3Config", "BusavikConfig", "FimudraConfig", "SezopelConfig", "Run", "LayerSpec", "architectures",
+__all__ = ["ModelSpec", "PartSpec", "Qwen3Config", "BusavikConfig", "FimudraConfig", "SezopelConfig", "LaralixConfig", "Run", "LayerSpec", "architectures",
            "config_of_folder", "register_architecture", "CacheError", "ConfigError",
            "InferError", "KernelError", "WeightsError", "SafeTensorsFolder",
            "write_random_model", "write_safetensors", "DecoderModel", "Engine", "Entry",

@@ -47,11 +47,14 @@ class Run:
     ``layer`` indexes ``ModelSpec.layers`` and may occur in several entries. ``cache_line`` is
     the line of the cache that the mixer of this run uses (``None``: the mixer keeps nothing).
     ``writes_cache`` is false for a run whose mixer reads a line that an earlier run wrote
-    (keys and values shared between layers).
+    (keys and values shared between layers). ``before`` names a part of the ``ENTRIES``
+    registry that changes the residual right before this run (what a pass through looped
+    layers adds to it).
     """
     layer: int
     cache_line: Optional[int] = None
     writes_cache: bool = True
+    before: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -25,7 +25,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
                       float scale, int vd, const float* __restrict__ sink, float softcap,
-                      const T* __restrict__ gate, int gate_stride) {
+                      const T* __restrict__ gate, int gate_stride,
+                      const float* __restrict__ slopes, int keep_first) {
   extern __shared__ __align__(16) float qs[];  // ATT_WARPS x hd
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -41,6 +42,10 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 
   int lo = 0;
   if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
+  // the first keep_first positions stay visible when the window has moved past them: the
+  // keys are walked in two runs, [0, kept) and [lo, pos]
+  const int kept = min(keep_first, lo);
+  const float slope = slopes ? slopes[h] : 0.f;
   // a sink: one more term exp(sink[h]) in the denominator, as a key of that score (not
   // scaled) whose value is zero
   float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
@@ -49,9 +54,11 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 #pragma unroll
   for (int d = 0; d < ATT_MAX_D; ++d) acc[d] = 0.f;
 
-  for (int k0 = lo; k0 <= pos; k0 += 32) {
+  for (int run = 0; run < 2; ++run) {
+  const int first = run ? lo : 0, last = run ? pos : kept - 1;
+  for (int k0 = first; k0 <= last; k0 += 32) {
     const int kp = k0 + lane;
-    const bool valid = kp <= pos;
+    const bool valid = kp <= last;
     size_t row = 0;
     float s = -INFINITY;
     if (valid) {
@@ -68,6 +75,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       }
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= slope * (float)(pos - kp);      // a bias that grows with the distance
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);  // 0 on the first tile (m = -inf)
@@ -76,7 +84,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 #pragma unroll
     for (int d = 0; d < ATT_MAX_D; ++d) acc[d] *= corr;
     m = m_new;
-    const int n = min(32, pos - k0 + 1);
+    const int n = min(32, last - k0 + 1);
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned lo32 = __shfl_sync(0xffffffffu, (unsigned)(row & 0xffffffffu), j);
@@ -102,6 +110,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         }
       }
     }
+  }
   }
   // a gate per head: the head's output times the sigmoid of the token's logit for this head
   const float inv = (gate ? 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])))
@@ -137,7 +146,8 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                         const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                         const int* __restrict__ seq_slot, int nh, int nkv, int hd, int window,
                         float scale, int vd, const float* __restrict__ sink, float softcap,
-                        const T* __restrict__ gate, int gate_stride) {
+                        const T* __restrict__ gate, int gate_stride,
+                        const float* __restrict__ slopes, int keep_first) {
   extern __shared__ __align__(16) float sm[];
   const int pitch = hd + 4, pieces = hd / 4, vpitch = vd + 4, vpieces = vd / 4;
   float* qs = sm;                                  // [ATT_WARPS][hd]
@@ -156,13 +166,19 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 
   int lo = 0;
   if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
+  // the first keep_first positions stay visible when the window has moved past them: the
+  // keys are walked in two runs, [0, kept) and [lo, pos]
+  const int kept = min(keep_first, lo);
+  const float slope = slopes ? slopes[h] : 0.f;
   float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
   float acc[ATT_MAX_D];
 #pragma unroll
   for (int d = 0; d < ATT_MAX_D; ++d) acc[d] = 0.f;
 
-  for (int k0 = lo; k0 <= pos; k0 += 32) {
-    const int n = min(32, pos - k0 + 1);
+  for (int run = 0; run < 2; ++run) {
+  const int first = run ? lo : 0, last = run ? pos : kept - 1;
+  for (int k0 = first; k0 <= last; k0 += 32) {
+    const int n = min(32, last - k0 + 1);
     __syncthreads();                               // the tile before has been read
     if (threadIdx.x < n)
       rows[threadIdx.x] = kv_row(page_table, max_pages, ring_pages, slot, k0 + threadIdx.x, nkv, g);
@@ -187,6 +203,7 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
       }
       s = dot * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= slope * (float)(pos - (k0 + lane));
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);
@@ -210,6 +227,7 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
       }
     }
   }
+  }
   // a gate per head: the head's output times the sigmoid of the token's logit for this head
   const float inv = (gate ? 1.0f / (1.0f + expf(-to_f32<T>(gate[(size_t)t * gate_stride + h])))
                           : 1.0f) / l;
@@ -228,14 +246,18 @@ attention_shared_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 // out + t * out_stride + h * vd. `vd`: the size of a value row (0: hd). `sink`: float32 [nh]
 // or null, one more term exp(sink[h]) in every softmax denominator of head h. `softcap` > 0:
 // every score s (after the scale) becomes softcap * tanh(s / softcap). `gate` (may be null):
-// head h's output of token t is multiplied by sigmoid(gate[t * gate_stride + h]).
+// head h's output of token t is multiplied by sigmoid(gate[t * gate_stride + h]). `slopes`:
+// float32 [nh] or null: slopes[h] * (query's position - key's position) is taken off every
+// score of head h after the cap. `keep_first` > 0: with a window, the first keep_first
+// positions of a sequence stay visible to every later one.
 MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_stride,
                                 const void* kpool, const void* vpool, int dtype,
                                 const int* page_table, int max_pages, int ring_pages,
                                 const int* tok_seq, const int* tok_pos, const int* seq_slot,
                                 int T, int nh, int nkv, int hd, int window, float scale,
                                 int vd, const float* sink, float softcap, const void* gate,
-                                int gate_stride, void* stream) {
+                                int gate_stride, const float* slopes, int keep_first,
+                                void* stream) {
   if (T <= 0) return 0;
   if (vd <= 0) vd = hd;
   if (hd <= 0 || hd > 1024 || vd > 32 * ATT_MAX_D)
@@ -264,7 +286,7 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
     attention_shared_kernel<T_><<<grid, ATT_WARPS * 32, shared, s>>>(                         \
         (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,     \
         page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window,   \
-        scale, vd, sink, softcap, (const T_*)gate, gate_stride);                                                               \
+        scale, vd, sink, softcap, (const T_*)gate, gate_stride, slopes, keep_first);                                                             \
   }
     if (dtype == MB_F32) GOS(float) else GOS(__nv_bfloat16)
 #undef GOS
@@ -274,7 +296,7 @@ MB_EXPORT int mb_attention_simt(const void* q, int q_stride, void* out, int out_
   attention_simt_kernel<T_, V_><<<grid, ATT_WARPS * 32, smem, s>>>(                           \
       (const T_*)q, q_stride, (T_*)out, out_stride, (const T_*)kpool, (const T_*)vpool,       \
       page_table, max_pages, ring_pages, tok_seq, tok_pos, seq_slot, nh, nkv, hd, window, scale, \
-      vd, sink, softcap, (const T_*)gate, gate_stride)
+      vd, sink, softcap, (const T_*)gate, gate_stride, slopes, keep_first)
   if (dtype == MB_F32) {
     if (vec) GO(float, true); else GO(float, false);
   } else {

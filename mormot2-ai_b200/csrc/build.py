@@ -52,6 +52,7 @@ SOURCES = {
     "latent_mma": "latent_mma.cu",
     "streams": "streams.cu",
     "recurrent": "recurrent.cu",
+    "linear_state": "linear_state.cu",
 }
 HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"gemm_tc": ["tc_common.cuh"],

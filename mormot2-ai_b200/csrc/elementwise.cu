@@ -432,6 +432,83 @@ MB_EXPORT int mb_add_bias(float* x, const void* b, int b_dtype, int T, int H, vo
   MB_CHECK_LAUNCH("mb_add_bias");
 }
 
+// ------------------------------------------------------------------ what a pass adds
+// x[t] += x0[t] + b for a pass through looped layers that starts from the residual plus the
+// embedding's output (x0, may be null) plus a vector of the pass (b [H]).
+template <typename TW>
+__global__ void pass_input_kernel(float* __restrict__ x, const float* __restrict__ x0,
+                                  const TW* __restrict__ b, int H) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  float* xr = x + (size_t)blockIdx.x * H;
+  const float* x0r = x0 ? x0 + (size_t)blockIdx.x * H : nullptr;
+  for (int c = threadIdx.x; c < H; c += blockDim.x)
+    xr[c] = (x0r ? xr[c] + x0r[c] : xr[c]) + to_f32<TW>(b[c]);
+}
+
+MB_EXPORT int mb_pass_input(float* x, const float* x0, const void* b, int b_dtype, int T, int H,
+                            void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (b_dtype == MB_F32)
+    mb_launch(pass_input_kernel<float>, dim3(T), dim3(256), 0, s, x, x0, (const float*)b, H);
+  else
+    mb_launch(pass_input_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, s, x, x0,
+              (const __nv_bfloat16*)b, H);
+  MB_CHECK_LAUNCH("mb_pass_input");
+}
+
+// ------------------------------------------------------------------ q and k normed as whole rows
+// Rows [q (qw) | k (kw) | room (kw)] of ld values: q <- wq * q / rms(q) over all qw values at
+// once, k likewise with wk; with copy_k the k values as they came are first copied behind k
+// (values that are the keys as projected). Without weights (null) only the copy is made. One block per token; sums in float32.
+template <typename T, typename TW>
+__global__ void wide_qk_norm_kernel(T* __restrict__ qkv, int ld, int qw, int kw,
+                                    const TW* __restrict__ wq, const TW* __restrict__ wk,
+                                    float eps, int copy_k) {
+  mb_grid_wait();
+  mb_grid_launch_next();
+  __shared__ float red[33];
+  T* row = qkv + (size_t)blockIdx.x * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < qw; c += blockDim.x) {
+    const float v = to_f32<T>(row[c]);
+    sq = fmaf(v, v, sq);
+  }
+  for (int c = threadIdx.x; c < kw; c += blockDim.x) {
+    const T raw = row[qw + c];
+    if (copy_k) row[qw + kw + c] = raw;
+    const float v = to_f32<T>(raw);
+    sk = fmaf(v, v, sk);
+  }
+  if (wq == nullptr) return;     // only the copy was asked for
+  sq = block_sum(sq, red);
+  __syncthreads();
+  sk = block_sum(sk, red);
+  const float iq = 1.0f / sqrtf(sq / (float)qw + eps), ik = 1.0f / sqrtf(sk / (float)kw + eps);
+  for (int c = threadIdx.x; c < qw; c += blockDim.x)
+    row[c] = from_f32<T>(to_f32<TW>(wq[c]) * (to_f32<T>(row[c]) * iq));
+  for (int c = threadIdx.x; c < kw; c += blockDim.x)
+    row[qw + c] = from_f32<T>(to_f32<TW>(wk[c]) * (to_f32<T>(row[qw + c]) * ik));
+}
+
+MB_EXPORT int mb_wide_qk_norm(void* qkv, int dtype, int ld, int T, int qw, int kw, const void* wq,
+                              const void* wk, int w_dtype, float eps, int copy_k, void* stream) {
+  if (T <= 0) return 0;
+  if (ld < qw + kw * (copy_k ? 2 : 1)) MB_FAIL("mb_wide_qk_norm: rows of %d values", ld);
+  cudaStream_t s = (cudaStream_t)stream;
+#define GO(T_, TW_)                                                                            \
+  mb_launch(wide_qk_norm_kernel<T_, TW_>, dim3(T), dim3(256), 0, s, (T_*)qkv, ld, qw, kw,       \
+            (const TW_*)wq, (const TW_*)wk, eps, copy_k)
+  if (dtype == MB_F32) {
+    if (w_dtype == MB_F32) GO(float, float); else GO(float, __nv_bfloat16);
+  } else {
+    if (w_dtype == MB_F32) GO(__nv_bfloat16, float); else GO(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef GO
+  MB_CHECK_LAUNCH("mb_wide_qk_norm");
+}
+
 // ------------------------------------------------------------------ a constant factor
 __global__ void scale_kernel(float* __restrict__ x, size_t total, float s) {
   mb_grid_wait();

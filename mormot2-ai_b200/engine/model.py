@@ -13,7 +13,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..errors import ConfigError
-from ..parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
+from ..parts import BLOCKS, EMBEDDINGS, ENTRIES, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS
 from ..parts.base import CacheNeed, StateNeed, TensorNeed
 from ..parts.block import settle
 
@@ -40,6 +40,13 @@ class DecoderModel:
         self.layers = [Layer(l, self.positions) for l in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm)
         self.head = HEADS.build(spec.head)
+        # what a run changes on the residual before its layer (a pass through looped layers)
+        self.entries = {i: ENTRIES.build(run.before) for i, run in enumerate(spec.schedule)
+                        if run.before is not None}
+        self.keeps_embedding = any(getattr(e, "add_embedding", False)
+                                   for e in self.entries.values())
+        if self.entries and spec.streams:
+            raise ConfigError("entries of runs are not defined for several residual streams")
         for i, run in enumerate(spec.schedule):
             if not 0 <= run.layer < len(self.layers):
                 raise ConfigError(f"entry {i} of the order names layer {run.layer} of "
@@ -49,6 +56,7 @@ class DecoderModel:
     # ---------------------------------------------------------------- what the model needs
     def parts(self):
         out = [self.embedding, self.final_norm, self.head] + list(self.positions.values())
+        out += list(self.entries.values())
         for l in self.layers:
             out += l.parts()
         return out
@@ -116,6 +124,10 @@ class DecoderModel:
             shape = (self.spec.streams,) + shape
         x = torch.empty(shape, dtype=torch.float32, device=self.rt.device)
         self.embedding.forward(step.tok_ids, x)
+        x0 = None
+        if self.keeps_embedding:     # a later pass adds the embedding's output once more
+            x0 = torch.empty_like(x)
+            self.embedding.forward(step.tok_ids, x0)
         if on_state:
             report, on_state = on_state, lambda name, x: report(name, x if x.dim() == 2 else x.sum(0))
             on_state("embed", x[0] if x.dim() == 3 else x)
@@ -124,6 +136,11 @@ class DecoderModel:
             line = cache.lines.get(run.cache_line) if run.cache_line is not None else None
             state = cache.states.get(run.cache_line) if run.cache_line is not None else None
             block = self.layers[run.layer].block
+            if i in self.entries:
+                if pending is not None:
+                    settle(x, pending)
+                    pending = None
+                self.entries[i].forward(x, x0)
             if getattr(block, "accepts_pending", False):
                 pending = block.forward(x, step, line, state, run.writes_cache, pending=pending)
             else:

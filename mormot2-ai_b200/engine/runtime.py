@@ -159,15 +159,17 @@ class Runtime:
         K.latent_attention(q, out, step, line, nh, kv_rank, rot_dim, window, scale)
 
     def attention(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd=0,
-                  sink=None, softcap=0.0, gate=None, gate_stride=0) -> None:
+                  sink=None, softcap=0.0, gate=None, gate_stride=0, slopes=None,
+                  keep_first=0) -> None:
         """``vd``: the size of a value row where it differs from ``hd``; ``sink``: float32
         [nh], one more term of every softmax denominator; ``softcap`` > 0: a cap
         c tanh(s / c) on the scaled scores; ``gate``: one logit per (token, head) whose sigmoid
-        multiplies the head's output."""
-        if self.fast_kernels and (not vd or vd == hd):
+        multiplies the head's output; ``slopes``: float32 [nh], taken off the scores times the
+        distance; ``keep_first``: positions at a sequence's start that a window never loses."""
+        if self.fast_kernels and (not vd or vd == hd) and slopes is None and not keep_first:
             from ..parts import attention_fast
             if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale,
                                   sink, softcap, gate, gate_stride):
                 return
         K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink,
-                         softcap, gate, gate_stride)
+                         softcap, gate, gate_stride, slopes, keep_first)

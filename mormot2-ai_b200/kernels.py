@@ -78,7 +78,9 @@ CLASS_OF = {"mb_gemm_tc": "products", "mb_gemm_simt": "products",
             "mb_mlstm_scan": "recurrence", "mb_tanh": "recurrence",
             "mb_retention_scan": "recurrence", "mb_retention_chunked": "recurrence",
             "mb_norm_add": "norms", "mb_cast_rows": "norms",
-            "mb_unary_act": "activation", "mb_softcap": "activation"}
+            "mb_unary_act": "activation", "mb_softcap": "activation",
+            "mb_pass_input": "embedding", "mb_wide_qk_norm": "rotary",
+            "mb_short_conv": "recurrence", "mb_linear_state_scan": "recurrence"}
 
 
 class Timing:
@@ -383,6 +385,33 @@ def scale_rows(x: torch.Tensor, factor: float) -> None:
           _stream())
 
 
+def pass_input(x: torch.Tensor, b: torch.Tensor, x0: Optional[torch.Tensor] = None) -> None:
+    """x[t, :] += x0[t, :] + b (x, x0 float32 [T, H]; b [H]): what a pass through looped layers
+    starts from."""
+    assert x.dtype == torch.float32 and b.numel() == x.shape[1] and b.is_contiguous()
+    _contig(x, "x")
+    if x0 is not None:
+        assert x0.dtype == torch.float32 and x0.shape == x.shape and x0.is_contiguous()
+    _call("elementwise", "mb_pass_input", [_vp, _vp, _vp, _i, _i, _i, _vp],
+          _ptr(x), _ptr(x0), _ptr(b), code_of(b.dtype), x.shape[0], x.shape[1], _stream())
+
+
+def wide_qk_norm(qkv: torch.Tensor, qw: int, kw: int, wq: torch.Tensor, wk: torch.Tensor,
+                 eps: float, copy_k: bool) -> None:
+    """Rows [q (qw) | k (kw) | ...]: q and k are each normed over their whole width with the
+    weights ``wq`` [qw] and ``wk`` [kw], in place; ``copy_k``: the k values as they came are
+    first copied into the kw columns behind k (without weights nothing else happens)."""
+    T, ld = qkv.shape
+    _contig(qkv, "qkv")
+    assert (wq is None and wk is None and copy_k) or (
+        wq.numel() == qw and wk.numel() == kw and wq.dtype == wk.dtype)
+    assert ld >= qw + kw * (2 if copy_k else 1)
+    _call("elementwise", "mb_wide_qk_norm", [_vp, _i, _i, _i, _i, _i, _vp, _vp, _i, _f, _i, _vp],
+          _ptr(qkv), code_of(qkv.dtype), ld, T, qw, kw, _ptr(wq), _ptr(wk),
+          code_of(wq.dtype) if wq is not None else F32,
+          float(eps), 1 if copy_k else 0, _stream())
+
+
 # ------------------------------------------------------------------------------ residual streams
 def _terms(terms):
     """[(y [T, H] float32, factor)] as the arrays the kernels take."""
@@ -565,6 +594,76 @@ def retention_scan(z: torch.Tensor, cols, decay: torch.Tensor, k_scale: float,
           0, _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out), _ptr(raw),
           code_of(out.dtype), T, step.B, heads, dim, vdim, _stream(),
           launches=1 if step.B * heads >= 96 else 2)
+
+
+def short_conv(z: torch.Tensor, col0: int, w: torch.Tensor, state: torch.Tensor, step,
+               out: torch.Tensor) -> None:
+    """out[t, c] = silu(sum_j w[c, j] * z[t - taps + 1 + j, col0 + c]) within each sequence;
+    the inputs before a step's first token come from ``state`` ([slots, >= (taps - 1) * C]
+    float32, a view whose rows may lie apart: zeros when a sequence starts), which afterwards
+    holds the step's last taps - 1 inputs (csrc/linear_state.cu)."""
+    T = z.shape[0]
+    C, taps = w.shape
+    assert z.dtype == torch.float32 and z.stride(1) == 1 and z.shape[1] >= col0 + C
+    assert w.dtype == torch.float32 and w.is_contiguous()
+    assert out.dtype == torch.float32 and out.shape == (T, C) and out.is_contiguous()
+    assert state.dtype == torch.float32 and state.stride(1) == 1
+    assert state.shape[1] >= (taps - 1) * C
+    _call("linear_state", "mb_short_conv",
+          [_vp, _i, _i, _vp, _i, _i, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+          _ptr(z), z.stride(0), col0, _ptr(w), taps, C, _ptr(state), state.stride(0), 0,
+          _ptr(step.tok_seq), _ptr(step.seq_start), _ptr(step.seq_slot), _ptr(out),
+          out.stride(0), T, step.B, _stream(), launches=2 if taps > 1 else 1)
+
+
+def linear_state_scan(mode: str, qkv: torch.Tensor, cols, group: int, gate: torch.Tensor,
+                      gate_col: int, normw: torch.Tensor, eps: float, state: torch.Tensor, step,
+                      out: torch.Tensor, heads: int, dim: int, vdim: int,
+                      decay_logits: Optional[torch.Tensor] = None, decay_col: int = 0,
+                      decay_bias: Optional[torch.Tensor] = None, inv_tau: float = 1.0,
+                      scalars: Optional[torch.Tensor] = None, beta_col: int = 0,
+                      rate_col: int = 0, a_log: Optional[torch.Tensor] = None,
+                      dt_bias: Optional[torch.Tensor] = None, unit_eps: float = 0.0) -> None:
+    """A matrix state per head walked token by token (csrc/linear_state.cu). ``qkv`` float32
+    [T, ld] with ``cols`` = the first columns of q, k and v in it; ``group`` heads share one q
+    and k. ``mode`` "gla": S <- diag(a) S + k v^T with a = sigmoid(decay_logits + decay_bias)
+    ^ inv_tau per key channel and q scaled by dim^(-1/2). ``mode`` "delta": q and k brought
+    to unit length (``unit_eps`` under the root; q also times dim^(-1/2)), S <- g S,
+    u = beta (v - S^T k), S <- S + k u^T with beta = sigmoid(scalars[beta_col + h]) and
+    g = exp(-exp(a_log[h]) softplus(scalars[rate_col + h] + dt_bias[h])). Then o = S^T q over its
+    root mean square, times ``normw`` [vdim], times silu(gate). The state row of a slot holds
+    heads x dim x vdim values."""
+    T = out.shape[0]
+    f32 = torch.float32
+    assert mode in ("gla", "delta") and len(cols) == 3
+    assert qkv.dtype == f32 and qkv.stride(1) == 1 and gate.dtype == f32 and gate.stride(1) == 1
+    assert normw.dtype == f32 and normw.numel() == vdim
+    _contig(out, "out")
+    assert out.shape == (T, heads * vdim) and state.dtype == f32 and state.stride(1) == 1
+    assert state.shape[1] >= heads * dim * vdim
+    if mode == "gla":
+        assert decay_logits.dtype == f32 and decay_logits.stride(1) == 1
+        assert decay_bias.dtype == f32 and decay_bias.numel() == heads * dim
+    else:
+        assert scalars.dtype == f32 and scalars.stride(1) == 1
+        assert a_log.dtype == f32 and a_log.numel() == heads
+        assert dt_bias.dtype == f32 and dt_bias.numel() == heads
+    # where a step has few (sequence, head) pairs a head's columns are dealt over several
+    # blocks, which leave their outputs here for the kernel that norms and gates them
+    sliced = step.B * heads < 96 and vdim > 32
+    raw = torch.empty((T, heads * vdim), dtype=f32, device=out.device)
+    _call("linear_state", "mb_linear_state_scan",
+          [_i, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _f, _vp, _i, _i, _i, _vp, _vp, _f,
+           _vp, _i, _i, _vp, _f, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+          0 if mode == "gla" else 1, _ptr(qkv), qkv.stride(0), *[int(c) for c in cols],
+          int(group), _ptr(decay_logits),
+          decay_logits.stride(0) if decay_logits is not None else 0, int(decay_col),
+          _ptr(decay_bias), float(inv_tau), _ptr(scalars),
+          scalars.stride(0) if scalars is not None else 0, int(beta_col), int(rate_col),
+          _ptr(a_log), _ptr(dt_bias), float(unit_eps), _ptr(gate), gate.stride(0), int(gate_col),
+          _ptr(normw), float(eps), _ptr(state), state.stride(0), 0, _ptr(step.seq_start),
+          _ptr(step.seq_slot), _ptr(out), _ptr(raw), code_of(out.dtype), T, step.B, heads, dim,
+          vdim, _stream(), launches=2 if sliced else 1)
 
 
 # ------------------------------------------------------------------------------ latent attention
@@ -783,23 +882,29 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int =
 def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv, hd,
                    window: int, scale: float, vd: int = 0,
                    sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                   gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
+                   gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
+                   slopes: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """``vd``: the size of a value row when it differs from ``hd``. ``sink``: float32 [nh],
     one more term exp(sink[h]) in the softmax denominators of head h. ``softcap`` > 0: scores
     become softcap * tanh(score / softcap). ``gate``: logits of q's type, head h of token t at
-    ``gate[t * gate_stride + h]``; the head's output is multiplied by their sigmoid."""
+    ``gate[t * gate_stride + h]``; the head's output is multiplied by their sigmoid.
+    ``slopes``: float32 [nh]; slopes[h] * (distance of key and query) is taken off head h's
+    scores after the cap. ``keep_first``: with a window, the first so many positions of a
+    sequence stay visible (the line must then keep all pages, not a ring)."""
     T = out.shape[0]
     _contig(out, "out")
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == nh)
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == nh)
     assert gate is None or gate.dtype == out.dtype
+    assert keep_first == 0 or line.ring_pages == 0
     _call("attention_simt", "mb_attention_simt",
           [_vp, _i, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f,
-           _i, _vp, _f, _vp, _i, _vp],
+           _i, _vp, _f, _vp, _i, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           code_of(out.dtype), _ptr(line.page_table), line.max_pages, line.ring_pages,
           _ptr(step.tok_seq), _ptr(step.tok_pos), _ptr(step.seq_slot), T, nh, nkv, hd,
           window, float(scale), vd or hd, _ptr(sink), float(softcap), _ptr(gate), gate_stride,
-          _stream())
+          _ptr(slopes), int(keep_first), _stream())
 
 
 # ------------------------------------------------------------------------------ sampling

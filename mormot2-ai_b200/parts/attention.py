@@ -12,7 +12,15 @@ c tanh(s / c) before the softmax; ``head_norm`` = "unit_after_rotation", which d
 by their root mean square (``head_norm_eps``) after the rotation, without a weight;
 ``names["g"]``, a projection to one logit per head whose sigmoid multiplies the head's output
 before the output projection (its rows ride along in the q/k/v product); ``shared_kv``: the
-mixer has no key and value projections and only ever reads the cache line of another layer.
+mixer has no key and value projections and only ever reads the cache line of another layer;
+``sink_value``: the sink as a constant, the same for every head (0: one more term exp(0) in
+the denominator); ``distance_exponent`` e: head h's scores lose 2^(e (h + 1) / heads) times the
+distance between query and key, after the cap; ``keep_first`` n with a ``window``: the first
+n positions of a sequence stay visible to all later ones (the cache line then keeps every
+page instead of a ring); ``head_norm`` = "whole_rows": q and k are each normed over their
+whole projection at once, with weights of that width; ``values`` = "keys_as_projected": there
+is no value projection, a token's values are its keys as they leave the projection (before any
+norm or rotation).
 """
 from __future__ import annotations
 
@@ -52,9 +60,27 @@ class GqaAttention(Part):
         if self.softcap < 0:
             raise ConfigError(f"a score cap of {self.softcap}")
         self.head_norm = p.get("head_norm", "weighted_before_rotation")
-        if self.head_norm not in ("weighted_before_rotation", "unit_after_rotation"):
+        if self.head_norm not in ("weighted_before_rotation", "unit_after_rotation",
+                                  "whole_rows"):
             raise ConfigError(f"head norm \"{self.head_norm}\" is not known (known: "
-                              "unit_after_rotation, weighted_before_rotation)")
+                              "unit_after_rotation, weighted_before_rotation, whole_rows)")
+        self.whole_rows = self.head_norm == "whole_rows"
+        if self.whole_rows and ("q_norm" not in self.names or self.head_norm_eps is None):
+            raise ConfigError("a norm over the whole rows of q and k has weights and an eps")
+        self.values = p.get("values", "projected")
+        if self.values not in ("projected", "keys_as_projected"):
+            raise ConfigError(f"values \"{self.values}\" (projected, keys_as_projected)")
+        self.v_from_k = self.values == "keys_as_projected"
+        if self.v_from_k and (self.vd != self.hd or "v" in self.names):
+            raise ConfigError("values that are the keys have the keys' size and no projection")
+        self.keep_first = int(p.get("keep_first") or 0)
+        if self.keep_first < 0 or (self.keep_first and not self.window):
+            raise ConfigError(f"keep_first = {self.keep_first} with a window of {self.window}")
+        self.sink_value = p.get("sink_value")
+        if self.sink_value is not None and "sink" in self.names:
+            raise ConfigError("a sink is either a constant or a tensor")
+        self.distance_exponent = p.get("distance_exponent")
+        self.slopes = None
         self.unit_after = self.head_norm == "unit_after_rotation"
         if self.unit_after and ("q_norm" in self.names or self.head_norm_eps is None):
             raise ConfigError("a unit norm after the rotation has an eps and no weights")
@@ -75,25 +101,36 @@ class GqaAttention(Part):
         n = self.names
         out = [TensorNeed(n["q"], (self.qw, self.hidden))]
         if not self.shared_kv:
-            out += [TensorNeed(n["k"], (self.kvw, self.hidden)),
-                    TensorNeed(n["v"], (self.vw, self.hidden))]
+            out.append(TensorNeed(n["k"], (self.kvw, self.hidden)))
+            if not self.v_from_k:
+                out.append(TensorNeed(n["v"], (self.vw, self.hidden)))
         out.append(TensorNeed(n["o"], (self.hidden, self.ow)))
         if self.gate_n:
             out.append(TensorNeed(n["g"], (self.nh, self.hidden)))
         if "sink" in n:
             out.append(TensorNeed(n["sink"], (self.nh,), "bias"))
         if "q_norm" in n:
-            out += [TensorNeed(n["q_norm"], (self.hd,), "vector"),
-                    TensorNeed(n["k_norm"], (self.hd,), "vector")]
+            out += [TensorNeed(n["q_norm"], (self.qw if self.whole_rows else self.hd,), "vector"),
+                    TensorNeed(n["k_norm"], (self.kvw if self.whole_rows else self.hd,), "vector")]
         return out
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(self.nkv, self.hd, self.window, 2, 0 if self.vd == self.hd else self.vd)
+        # kept first positions lie outside a ring of the window's pages: such a line keeps all
+        return CacheNeed(self.nkv, self.hd, 0 if self.keep_first else self.window, 2,
+                         0 if self.vd == self.hd else self.vd)
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.rt = rt
         plain = (self.vd == self.hd and "sink" not in self.names and not self.softcap
-                 and not self.gate_n and not self.unit_after)
+                 and not self.gate_n and not self.unit_after and self.sink_value is None
+                 and self.distance_exponent is None)
+        if self.sink_value is not None:
+            self.sink = torch.full((self.nh,), float(self.sink_value), dtype=torch.float32,
+                                   device=rt.device)
+        if self.distance_exponent is not None:
+            e = float(self.distance_exponent)
+            self.slopes = torch.tensor([2.0 ** (e * (h + 1) / self.nh) for h in range(self.nh)],
+                                       dtype=torch.float32, device=rt.device)
         if (plain and (self.hd % 16 or self.hd > 256)) or self.hd > 1024 or self.vd > 256:
             raise KernelError(
                 f"heads of {self.hd} values (value rows of {self.vd}) are not supported by the "
@@ -113,7 +150,10 @@ class GqaAttention(Part):
             self.o = Linear(weights[n["o"]], rt)
             self.q_norm = self.k_norm = None
             return
-        wq, wk, wv = weights[n["q"]], weights[n["k"]], weights[n["v"]]
+        wq, wk = weights[n["q"]], weights[n["k"]]
+        # values that are the keys: the product has no rows for them; the kernel that norms q
+        # and k copies the keys as they came into the value columns of the row
+        wv = wk[:0] if self.v_from_k else weights[n["v"]]
         if wg is not None and not (wq.dtype == wk.dtype == wv.dtype == wg.dtype):
             wq, wk, wv, wg = wq.float(), wk.float(), wv.float(), wg.float()
         if wq.dtype == wk.dtype == wv.dtype:
@@ -128,7 +168,7 @@ class GqaAttention(Part):
                 # so that loading never holds much more than the model
                 del wq, wk, wv
                 for key in ("q", "k", "v"):
-                    weights.pop(n[key], None)
+                    weights.pop(n.get(key, ""), None)
         else:
             self.qkv = None
             self.split = [Linear(wq, rt), Linear(wk, rt), Linear(wv, rt)]
@@ -166,7 +206,9 @@ class GqaAttention(Part):
                              else (None, 0))
         split_ok = (writes_cache and self.qkv is not None and rot_dim == self.hd
                     and self.hd in (64, 128, 256) and self.rt.dtype == torch.bfloat16
-                    and self.vd == self.hd and not self.gate_n)
+                    and self.vd == self.hd and not self.gate_n and not self.whole_rows
+                    and not self.v_from_k)
+        more = {"slopes": self.slopes, "keep_first": self.keep_first}
         qkv = self.qkv(h, defer=True) if split_ok else None
         if isinstance(qkv, Pending):
             # the kernel that norms and rotates q and k adds the split sums up as it reads them
@@ -176,27 +218,43 @@ class GqaAttention(Part):
                                  unit_after=self.unit_after)
             attn = torch.empty((T, self.qw), dtype=self.rt.dtype, device=h.device)
             self.rt.attention(q, self.qw, attn, step, line, self.nh, self.nkv, self.hd,
-                              self.window, self.scale, sink=self.sink, softcap=self.softcap)
+                              self.window, self.scale, sink=self.sink, softcap=self.softcap,
+                              **more)
             return self._project(attn, x, store)
         if qkv is not None:
             pass
         elif not writes_cache:
             qkv = self.q_only(h)
+        elif self.qkv is not None and self.v_from_k:
+            # room for the values behind the keys, which the product does not fill
+            qkv = torch.empty((T, width), dtype=self.rt.dtype, device=h.device)
+            self.qkv(h, out=qkv[:, :self.qw + self.kvw])
         elif self.qkv is not None:
             qkv = self.qkv(h)
         else:
             qkv = torch.empty((T, width), dtype=self.rt.dtype, device=h.device)
             self.split[0](h, out=qkv[:, :self.qw])
             self.split[1](h, out=qkv[:, self.qw:self.qw + self.kvw])
-            self.split[2](h, out=qkv[:, self.qw + self.kvw:])
-        K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, eps, inv_freq, rot_dim,
+            if not self.v_from_k:
+                self.split[2](h, out=qkv[:, self.qw + self.kvw:])
+        q_norm, k_norm = self.q_norm, self.k_norm
+        if self.whole_rows or self.v_from_k:
+            if not writes_cache:
+                raise ConfigError("whole-row norms and values from keys with a borrowed cache line")
+            if self.whole_rows:
+                K.wide_qk_norm(qkv, self.qw, self.kvw, q_norm, k_norm, eps, self.v_from_k)
+                q_norm = k_norm = None
+            else:       # the copy alone; the per-head norm and the rotation follow as ever
+                K.wide_qk_norm(qkv, self.qw, self.kvw, None, None, eps, True)
+        K.qk_norm_rope_store(qkv, q_norm, k_norm, eps, inv_freq, rot_dim,
                              step, line, self.nh, nkv, self.hd, writes_cache, vd=self.vd,
                              unit_after=self.unit_after)
         attn = torch.empty((T, self.ow), dtype=self.rt.dtype, device=h.device)
         self.rt.attention(qkv, width, attn, step, line, self.nh, self.nkv, self.hd,
                           self.window, self.scale, vd=self.vd, sink=self.sink,
                           softcap=self.softcap,
-                          gate=qkv[:, heads_width:] if self.gate_n else None, gate_stride=width)
+                          gate=qkv[:, heads_width:] if self.gate_n else None, gate_stride=width,
+                          **more)
         return self._project(attn, x, store)
 
     def _project(self, attn, x, store: bool):

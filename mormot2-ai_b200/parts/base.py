@@ -129,6 +129,7 @@ NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
+ENTRIES = Registry("entry of a run")
 HEADS = Registry("head")
 
 

@@ -10,7 +10,7 @@ from typing import Dict, List
 import torch
 
 from .. import kernels as K
-from .base import EMBEDDINGS, HEADS, Part, TensorNeed
+from .base import EMBEDDINGS, ENTRIES, HEADS, Part, TensorNeed
 from .linear import Linear
 
 
@@ -66,5 +66,29 @@ class LmHead(Part):
         return logits
 
 
+class PassInput(Part):
+    """What a pass through looped layers adds to the residual before its first layer: row
+    ``row`` of the table ``name`` [rows, size] and, with ``add_embedding``, the embedding's
+    output once more (the model keeps a copy of it for the runs that ask)."""
+    capturable = True
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.name = prefix + p["name"]
+        self.rows, self.row, self.size = int(p["rows"]), int(p["row"]), int(p["size"])
+        self.add_embedding = bool(p.get("add_embedding", False))
+
+    def tensors(self) -> List[TensorNeed]:
+        return [TensorNeed(self.name, (self.rows, self.size), "bias")]
+
+    def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.vector = weights[self.name][self.row].contiguous()
+
+    def forward(self, x: torch.Tensor, x0) -> None:
+        K.pass_input(x, self.vector, x0 if self.add_embedding else None)
+
+
 EMBEDDINGS.register("token_embedding", TokenEmbedding)
+ENTRIES.register("pass_input", PassInput)
 HEADS.register("lm_head", LmHead)

@@ -69,14 +69,24 @@ class LatentAttention(Part):
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.rt = rt
         n = self.names
-        first = [weights[n["dq"]], weights[n["dkv"]]] + ([weights[n["g"]]] if self.gated else [])
+        w_dkv, w_uq = weights[n["dkv"]], weights[n["uq"]]
+        if getattr(self.position, "pairing", "half") == "neighbours" and self.rd:
+            # an encoding that turns neighbours: the rows that produce the shared key part and
+            # every head's rotated query part are reordered once, so that the kernels' pairing
+            # (i, i + half) turns the same pairs; the scores see no difference
+            order = torch.tensor(self.position.half_order(self.rd), device=w_dkv.device)
+            w_dkv = torch.cat([w_dkv[:self.kvr], w_dkv[self.kvr:][order]], dim=0)
+            per = w_uq.view(self.nh, self.dim + self.rd, self.qr)
+            w_uq = torch.cat([per[:, :self.dim], per[:, self.dim:][:, order]],
+                             dim=1).reshape(w_uq.shape)
+        first = [weights[n["dq"]], w_dkv] + ([weights[n["g"]]] if self.gated else [])
         if len({w.dtype for w in first}) > 1:
             first = [w.float() for w in first]
         # one product for everything that reads h; the query latent first, then the key/value
         # latent with the shared key part behind it, then the gate
         self.down = Linear(torch.cat(first, dim=0), rt)
         self.kv_col, self.gate_col = self.qr, self.qr + self.kvr + self.rd
-        self.uq = Linear(weights[n["uq"]], rt)
+        self.uq = Linear(w_uq, rt)
         # per head: W_uk,hᵀ as [kv_rank, dim] (the product's output rows), W_uv,h as [vdim, kv_rank]
         self.uk_t = (weights[n["uk"]].view(self.nh, self.dim, self.kvr).transpose(1, 2)
                      .contiguous())

@@ -1,5 +1,7 @@
 """RMSNorm: y = w · x / sqrt(mean(x²) + eps), the weight multiplying as it is (not 1 + w);
-sums in float32 (``backend.cpu.pas:1769-1795``, ``ops.cu:116-130`` of the reference).
+sums in float32 (``backend.cpu.pas:1769-1795``, ``ops.cu:116-130`` of the reference). With
+``one_plus`` the stored weight lies around zero and 1 + w multiplies (formed once at load, in
+float32).
 
 Dynamic Tanh: y = tanh(alpha · x) · w + b with a learned scalar alpha: a norm that forms no
 mean and no variance, value by value in float32.
@@ -25,13 +27,16 @@ class RmsNorm(Part):
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.name = prefix + spec.params["name"]
+        self.one_plus = bool(spec.params.get("one_plus", False))
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> List[TensorNeed]:
-        return [TensorNeed(self.name, (self.size,), "vector")]
+        return [TensorNeed(self.name, (self.size,), "around_zero" if self.one_plus else "vector")]
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
         self.weight = weights[self.name]
+        if self.one_plus:
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
         self.rt = rt
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,

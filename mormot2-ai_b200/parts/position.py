@@ -8,6 +8,12 @@ reference does (``decoder.pas:1733-1736``; angles ``:2539-2561``); with ``roundi
 the frequencies theta^(−2i / rot_dim) are formed in float64 and rounded to float32 once.
 ``none`` rotates nothing.
 
+``rope_pairs`` has the same frequencies and angles but turns neighbours: value 2i with value
+2i + 1. A mixer whose rotated values only ever meet in a dot product of two vectors turned the
+same way (queries and keys) may serve it with the rotate-half kernels by reordering the rows
+of the projections that produce those values once at load: ``half_order()`` gives the order
+(old index of every new place) that makes pair i land on the places i and i + rot_dim/2.
+
 ``rope_yarn`` is the same rotation with YaRN's frequencies: with
 d(t) = dims · ln(original / (2π t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
 hi = min(ceil(d(slow)), dims − 1) and ramp_i = clamp((i − lo) / max(hi − lo, 0.001), 0, 1),
@@ -67,6 +73,19 @@ class RopeHalf(Part):
 
     def frequencies(self) -> Tuple[Optional[torch.Tensor], int]:
         return self.inv_freq, self.rot_dim
+
+
+class RopePairs(RopeHalf):
+    pairing = "neighbours"
+
+    def half_order(self, size: int) -> list:
+        """For a vector of ``size`` values whose first ``rot_dim`` turn as neighbours: the
+        order [0, 2, 4, ..., 1, 3, 5, ..., rest] in which the rotate-half pairing turns the
+        same pairs by the same angles."""
+        r = self.rot_dim
+        if size < r:
+            raise ConfigError(f"{r} rotating values of a vector of {size}")
+        return list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, size))
 
 
 def yarn_inverse_frequencies(theta: float, rot_dim: int, factor: float, original: float,
@@ -138,6 +157,7 @@ class NoPosition(Part):
 
 
 POSITIONS.register("rope_half", RopeHalf)
+POSITIONS.register("rope_pairs", RopePairs)
 POSITIONS.register("rope_yarn", RopeYarn)
 POSITIONS.register("rope_scaled_bands", RopeScaledBands)
 POSITIONS.register("none", NoPosition)

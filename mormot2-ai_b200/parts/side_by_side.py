@@ -1,7 +1,11 @@
 """Several mixers side by side: all read the same input, and the result is the sum of their
 outputs with a constant factor each. A branch is any registered mixer; at most one of them
 may keep keys and values (it gets the cache line), and the branches' fixed-size states lie one
-after another in the state of this mixer."""
+after another in the state of this mixer.
+
+A branch may name ``out_norm`` = {"name", "eps"}: its output is then brought to unit root mean
+square over the model width and multiplied by that weight [hidden] before its factor applies
+(the factor is folded into the weight once at load)."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional
@@ -19,11 +23,18 @@ class SideBySide(Part):
 
     def __init__(self, spec, prefix: str = "", positions=None):
         super().__init__(spec, prefix)
-        self.branches, self.scales = [], []
+        self.branches, self.scales, self.out_norms = [], [], []
         for b in spec.params["branches"]:
             sub = b["mixer"] if isinstance(b["mixer"], PartSpec) else PartSpec(**b["mixer"])
             self.branches.append(MIXERS.build(sub, prefix, positions=positions))
             self.scales.append(float(b.get("scale", 1.0)))
+            norm = b.get("out_norm")
+            self.out_norms.append((prefix + norm["name"], float(norm["eps"])) if norm else None)
+        if any(self.out_norms) and not all(self.out_norms):
+            raise ConfigError("either every mixer side by side has an output norm or none")
+        self.hidden = int(spec.params.get("hidden_size", 0))
+        if any(self.out_norms) and self.hidden <= 0:
+            raise ConfigError("output norms of mixers side by side need hidden_size")
         if not 1 <= len(self.branches) <= 4:
             raise ConfigError(f"{len(self.branches)} mixers side by side (1 to 4)")
         if sum(b.cache_need() is not None for b in self.branches) > 1:
@@ -45,13 +56,15 @@ class SideBySide(Part):
         return all(getattr(b, "capturable", False) for b in self.branches)
 
     def libraries(self, rt) -> List[str]:
-        out = ["streams"]
+        out = [] if any(self.out_norms) else ["streams"]
         for b in self.branches:
             out += [n for n in b.libraries(rt) if n not in out]
         return out
 
     def tensors(self) -> List[TensorNeed]:
-        return [t for b in self.branches for t in b.tensors()]
+        out = [t for b in self.branches for t in b.tensors()]
+        out += [TensorNeed(n[0], (self.hidden,), "vector") for n in self.out_norms if n]
+        return out
 
     def cache_need(self) -> Optional[CacheNeed]:
         for b in self.branches:
@@ -66,6 +79,9 @@ class SideBySide(Part):
         self.rt = rt
         for b in self.branches:
             b.bind(weights, rt)
+        # a branch's factor rides in its norm's weight (float32)
+        self.norm_weights = [(weights[n[0]].to(torch.float32) * s).contiguous() if n else None
+                             for n, s in zip(self.out_norms, self.scales)]
 
     def forward_branches(self, h, step, line, state, writes_cache: bool):
         """Runs every branch and returns ``[(y_b float32 [T, hidden], factor_b)]``: whoever
@@ -96,7 +112,35 @@ class SideBySide(Part):
         return terms
 
     def forward(self, h, x, step, line, state, writes_cache: bool, store: bool = False):
+        if any(self.out_norms):
+            return self._forward_normed(h, x, step, line, state, writes_cache, store)
         K.add_scaled(x, self.forward_branches(h, step, line, state, writes_cache), store)
+        return None
+
+    def _forward_normed(self, h, x, step, line, state, writes_cache: bool, store: bool):
+        """x += factor_b * w_b * y_b / rms(y_b) for every branch: one kernel a branch sums the
+        branch's split sums (if its output product left any), norms the row and adds it."""
+        if store:
+            raise ConfigError("mixers side by side with output norms add into the residual")
+        for b, (at, n), norm, w in zip(self.branches, self.offsets, self.out_norms,
+                                       self.norm_weights):
+            sub_state = state[:, at:at + n] if n else None
+            sub_line = line if b.cache_need() is not None else None
+            y = torch.empty((h.shape[0], h.shape[1]), dtype=torch.float32, device=h.device)
+            if getattr(b, "can_store", False):
+                pending = b.forward(h, y, step, sub_line, sub_state, writes_cache, store=True)
+                if pending is not None and pending.partial.shape[0] <= 8:
+                    K.norm_add(pending.partial, w, norm[1], x)
+                    continue
+                if pending is not None:
+                    y.zero_()
+                    K.add_partials(y, pending.partial)
+            else:
+                y.zero_()
+                pending = b.forward(h, y, step, sub_line, sub_state, writes_cache)
+                if pending is not None:
+                    K.add_partials(y, pending.partial)
+            K.norm_add(y, w, norm[1], x)
         return None
 
 

@@ -38,6 +38,10 @@ def random_tensors(needs: Iterable[TensorNeed], seed: int, std: float = 0.02,
             t = torch.empty(n.shape, dtype=dtype, device=device).normal_(0.0, 1.0, generator=gen)
         if n.role == "vector":
             t = t.mul_(norm_std).add_(1.0)
+        elif n.role == "taps":
+            t = t.mul_(0.5)
+        elif n.role == "around_zero":
+            t = t.mul_(norm_std)
         elif n.role == "fraction":
             t = t.mul_(0.7071).erf_().add_(1.0).mul_(0.5)      # a normal draw made uniform
         elif n.role == "identity":
