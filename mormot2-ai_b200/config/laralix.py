@@ -24,7 +24,9 @@ of ``conv`` taps.
 ``parallel_2``: ``left_scale`` * left + ``right_scale`` * right. Left: grouped-query attention
 whose values are the keys as projected, q and k normed over their whole rows, a window
 ``mask.size`` that also keeps the first ``mask.keep_first`` positions. Right: gated linear
-attention with a decay per key channel, sigmoid(.)^(1 / ``tau``).
+attention with a decay per key channel, sigmoid(.)^(1 / ``tau``); the low rank of the decay's
+two projections is read from the stored tensors (``rank``, if present, names it for a model
+of random weights).
 
 ``latent_attention``: queries through a latent of ``q_rank``, keys and values from a latent of
 ``kv_rank`` and a shared rotated key part of ``rot_dim`` values; ``rot.dims`` of them turn, in
@@ -126,7 +128,7 @@ class LaralixConfig:
         size = _int(mk, "size", source + " mask", hi=1 << 24) if mk.get("size") is not None else 0
         keep = (_int(mk, "keep_first", source + " mask", lo=0, hi=1 << 24)
                 if mk.get("keep_first") is not None else 0)
-        return size, keep
+        return size, (keep if size else 0)    # without a window every position is visible anyway
 
     @classmethod
     def _check_layer(cls, layer: Any, source: str) -> None:
@@ -211,16 +213,15 @@ class LaralixConfig:
         params: Dict[str, Any] = {
             "hidden_size": self.width, "heads": heads,
             "kv_heads": int(m.get("kv_heads") or heads), "head_dim": int(m["dim"]),
-            "scale": float(m["scale"]), "window": size, "head_norm_eps": self.norm_eps,
-            "names": names}
+            "scale": float(m["scale"]), "window": size, "keep_first": keep,
+            "head_norm_eps": self.norm_eps, "names": names}
         if kind == "parallel":
             names["v"] = prefix + "v"
             params.update({"v_dim": int(m.get("vdim") or m["dim"]),
                            "softcap": float(m.get("softcap") or 0.0),
                            "distance_exponent": DISTANCE_EXPONENT, "sink_value": 0.0})
         else:
-            params.update({"head_norm": "whole_rows", "values": "keys_as_projected",
-                           "keep_first": keep})
+            params.update({"head_norm": "whole_rows", "values": "keys_as_projected"})
         return PartSpec("gqa_attention", params)
 
     def _mixer(self, layer: Dict[str, Any], positions: Dict[str, PartSpec]) -> PartSpec:
@@ -267,6 +268,9 @@ class LaralixConfig:
             rec = PartSpec("gated_linear_attention", {
                 "hidden_size": c.width, "heads": heads, "dim": dim, "vdim": vdim,
                 "tau": float(right["tau"]), "eps": c.norm_eps,
+                # the decay's low rank is what the stored tensors have; a configuration that a
+                # random model is drawn from names it as "rank"
+                "decay_rank": int(right["rank"]) if right.get("rank") is not None else None,
                 "names": {k: r + v for k, v in {
                     "q": "q", "k": "k", "v": "v", "g": "g", "a1": "a1", "a2": "a2",
                     "a2_bias": "a2.b", "norm": "norm", "o": "o"}.items()}})
@@ -286,6 +290,9 @@ class LaralixConfig:
             norms = {"mixer": norm("norm1")}
             if mlp is None:
                 ff = PartSpec("none")
+                # a layer without a feed-forward may still store its second norm: tolerated, unused
+                norms["spare"] = PartSpec("rmsnorm", {"name": "norm2", "size": c.width,
+                                                      "eps": c.norm_eps, "optional": True})
             else:
                 ff = PartSpec("swiglu", {"hidden_size": c.width,
                                          "intermediate_size": int(mlp["ff"]),

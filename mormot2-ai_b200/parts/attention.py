@@ -123,7 +123,8 @@ class GqaAttention(Part):
         self.rt = rt
         plain = (self.vd == self.hd and "sink" not in self.names and not self.softcap
                  and not self.gate_n and not self.unit_after and self.sink_value is None
-                 and self.distance_exponent is None)
+                 and self.distance_exponent is None and not self.whole_rows
+                 and not self.v_from_k and not self.keep_first)
         if self.sink_value is not None:
             self.sink = torch.full((self.nh,), float(self.sink_value), dtype=torch.float32,
                                    device=rt.device)

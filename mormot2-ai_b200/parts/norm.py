@@ -28,12 +28,17 @@ class RmsNorm(Part):
         self.eps = float(spec.params["eps"])
         self.name = prefix + spec.params["name"]
         self.one_plus = bool(spec.params.get("one_plus", False))
+        self.optional = bool(spec.params.get("optional", False))   # may be absent (and unused)
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> List[TensorNeed]:
-        return [TensorNeed(self.name, (self.size,), "around_zero" if self.one_plus else "vector")]
+        return [TensorNeed(self.name, (self.size,), "around_zero" if self.one_plus else "vector",
+                           optional=self.optional)]
 
     def bind(self, weights: Dict[str, torch.Tensor], rt) -> None:
+        self.rt = rt
+        if self.optional and self.name not in weights:
+            return
         self.weight = weights[self.name]
         if self.one_plus:
             self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
