@@ -140,7 +140,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    int nkv, int window, float scale_log2, float* __restrict__ part_o,
                    float* __restrict__ part_ml, bf16* __restrict__ out, int out_stride,
                    int in_clusters, int* __restrict__ error, const float* __restrict__ sink,
-                   float cap_log2, const bf16* __restrict__ gate, int gate_stride) {
+                   float cap_log2, const bf16* __restrict__ gate, int gate_stride,
+                   const float* __restrict__ slopes, int keep_first) {
   constexpr int CH = HD / 32;  // 32-dim chunks of q·k
   constexpr int DB = HD / 64;  // 64-dim blocks of p·v
   constexpr uint32_t TILE = MB_PAGE * HD * 2;  // bytes of a page's keys (or values)
@@ -163,8 +164,14 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   const int pos = tok_pos[t];
   const int slot = tok_slot[t];
   const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-  const int p_first = lo / MB_PAGE + s, p_last = pos / MB_PAGE;
-  const int n_pages = p_first <= p_last ? (p_last - p_first) / S + 1 : 0;  // p_first + i * S
+  // the pages of the sequence that hold visible keys: those of the first keep_first positions
+  // that the window has left behind (kp of them, from page 0), then the window's; the splits
+  // take every S-th entry of that list
+  const int lo_page = lo / MB_PAGE, p_last = pos / MB_PAGE;
+  const int kp = min((min(keep_first, lo) + MB_PAGE - 1) / MB_PAGE, lo_page);
+  const int listed = kp + p_last - lo_page + 1;
+  const int n_pages = s < listed ? (listed - 1 - s) / S + 1 : 0;           // entries s + i * S
+  auto page_at = [&](int i) { const int j = s + i * S; return j < kp ? j : lo_page + j - kp; };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < DEC_STAGES; ++i) {
@@ -196,7 +203,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     for (int i0 = 0; i0 < n_pages; i0 += 32) {
       int mine = 0;
       if (i0 + lane < n_pages) {
-        const int p = p_first + (i0 + lane) * S;
+        const int p = page_at(i0 + lane);
         const int entry = ring_pages > 0 ? p % ring_pages : p;
         mine = MB_INDEX_OK(entry < max_pages, 1, slot, p, max_pages)
                    ? page_table[(size_t)slot * max_pages + entry] : 0;
@@ -205,7 +212,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       const int n = min(32, n_pages - i0);
       for (int i = 0; i < n; ++i) {
         const int page = __shfl_sync(0xffffffffu, mine, i);
-        if (!waited && p_first + (i0 + i) * S == p_last) {
+        if (!waited && page_at(i0 + i) == p_last) {
           mb_grid_wait();
           waited = true;
         }
@@ -229,10 +236,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       load_q<HD>(r < rows_valid ? qrow : nullptr, r + 8 < rows_valid ? qrow + 8 * HD : nullptr, c,
                  qa, qb);
     }
+    // a bias that grows with the distance (in units of log2 e, as the scores are)
+    const float sl0 = slopes && r < rows_valid ? slopes[h0 + r] * 1.4426950408889634f : 0.f;
+    const float sl1 = slopes && r + 8 < rows_valid ? slopes[h0 + r + 8] * 1.4426950408889634f : 0.f;
     int st = 0;
     uint32_t ph = 0;
     for (int i = 0; i < n_pages; ++i) {
-      const int key0 = (p_first + i * S) * MB_PAGE + 16 * warp;  // this warp's 16 keys
+      const int key0 = page_at(i) * MB_PAGE + 16 * warp;  // this warp's 16 keys
       mbar_wait(full0 + 8 * st, ph, error, 5);
       const uint32_t ks = tiles + st * 2 * TILE + (uint32_t)(16 * warp) * HD * 2;
       const uint32_t vs = ks + TILE;
@@ -254,9 +264,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + u * 8 + 2 * c + e;
-          const bool ok = key >= lo && key <= pos;
-          sc[u][e] = ok ? score_log2<CAP>(sc[u][e], scale_log2, cap_log2) : -INFINITY;
-          sc[u][2 + e] = ok ? score_log2<CAP>(sc[u][2 + e], scale_log2, cap_log2) : -INFINITY;
+          const bool ok = key <= pos && (key >= lo || key < keep_first);
+          const float far = (float)(pos - key);
+          sc[u][e] = ok ? score_log2<CAP>(sc[u][e], scale_log2, cap_log2) - sl0 * far : -INFINITY;
+          sc[u][2 + e] = ok ? score_log2<CAP>(sc[u][2 + e], scale_log2, cap_log2) - sl1 * far
+                            : -INFINITY;
           mx0 = fmaxf(mx0, sc[u][e]);
           mx1 = fmaxf(mx1, sc[u][2 + e]);
         }
@@ -455,7 +467,8 @@ static int decode_launch(const void* q, int q_stride, void* out, int out_stride,
                          int T, int nh, int nkv, int hd, int window, float scale, int splits,
                          float* part_o, float* part_ml, int in_clusters, int* error,
                          cudaStream_t s, const float* sink = nullptr, float softcap = 0.f,
-                         const void* gate = nullptr, int gate_stride = 0) {
+                         const void* gate = nullptr, int gate_stride = 0,
+                         const float* slopes = nullptr, int keep_first = 0) {
   const int G = nh / nkv, subs = (G + 15) / 16;
   const float log2e = 1.4426950408889634f;
   const float scale_log2 = softcap > 0.f ? 2.f * log2e * scale / softcap : scale * log2e;
@@ -476,13 +489,14 @@ static int decode_launch(const void* q, int q_stride, void* out, int out_stride,
                          smem, s, splits, (const bf16*)q, q_stride, (const bf16*)kpool,        \
                          (const bf16*)vpool, page_table, max_pages, ring_pages, tok_slot,      \
                          tok_pos, nh, nkv, window, scale_log2, part_o, part_ml, (bf16*)out,    \
-                         out_stride, 1, error, sink, cap_log2, (const bf16*)gate, gate_stride);\
+                         out_stride, 1, error, sink, cap_log2, (const bf16*)gate, gate_stride, \
+                         slopes, keep_first);                                                  \
     } else {                                                                                   \
       mb_launch(attn_decode_kernel<HD_, CAP_>, grid, dim3((DEC_WARPS + 1) * 32), smem, s,      \
                 (const bf16*)q, q_stride, (const bf16*)kpool, (const bf16*)vpool, page_table,  \
                 max_pages, ring_pages, tok_slot, tok_pos, nh, nkv, window, scale_log2, part_o, \
                 part_ml, (bf16*)out, out_stride, in_clusters, error, sink, cap_log2,           \
-                (const bf16*)gate, gate_stride);                                               \
+                (const bf16*)gate, gate_stride, slopes, keep_first);                           \
       if (!in_clusters)                                                                        \
         mb_launch(attn_merge_kernel<HD_>, mgrid, dim3(HD_), 0, s, (const float*)part_o,        \
                   (const float*)part_ml, splits, (bf16*)out, out_stride, nh,                   \
@@ -512,7 +526,7 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
                                   int hd, int window, float scale, int splits, float* scratch,
                                   long long scratch_floats, int* error, const float* sink,
                                   float softcap, const void* gate, int gate_stride,
-                                  void* stream) {
+                                  const float* slopes, int keep_first, void* stream) {
   if (T <= 0) return 0;
   if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
   const long long need = mb_attention_decode_scratch(T, nh, hd, splits);
@@ -521,7 +535,8 @@ MB_EXPORT int mb_attention_decode(const void* q, int q_stride, void* out, int ou
   return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                        ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
                        scratch, scratch + (size_t)T * nh * splits * hd, 0, error,
-                       (cudaStream_t)stream, sink, softcap, gate, gate_stride);
+                       (cudaStream_t)stream, sink, softcap, gate, gate_stride, slopes,
+                       keep_first);
 }
 
 // The same with the splits of a (token, group of heads) as the CTAs of one thread-block
@@ -536,7 +551,7 @@ MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* ou
                                            int nh, int nkv, int hd, int window, float scale,
                                            int splits, int* error, const float* sink,
                                            float softcap, const void* gate, int gate_stride,
-                                           void* stream) {
+                                           const float* slopes, int keep_first, void* stream) {
   if (T <= 0) return 0;
   if (decode_checks(q, q_stride, kpool, vpool, T, nh, nkv, hd, splits)) return -1;
   if (splits > MB_DECODE_CLUSTER_SPLITS)
@@ -546,7 +561,7 @@ MB_EXPORT int mb_attention_decode_clusters(const void* q, int q_stride, void* ou
   return decode_launch(q, q_stride, out, out_stride, kpool, vpool, page_table, max_pages,
                        ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window, scale, splits,
                        nullptr, nullptr, 1, error, (cudaStream_t)stream, sink, softcap, gate,
-                       gate_stride);
+                       gate_stride, slopes, keep_first);
 }
 
 // ------------------------------------------------------------------ prefill
@@ -625,7 +640,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     int max_pages, int ring_pages, const int* __restrict__ seq_start,
                     const int* __restrict__ seq_past, const int* __restrict__ seq_slot, int nh,
                     int nkv, int window, float scale_log2, const float* __restrict__ sink,
-                    float cap_log2, const bf16* __restrict__ gate, int gate_stride) {
+                    float cap_log2, const bf16* __restrict__ gate, int gate_stride,
+                    const float* __restrict__ slopes, int keep_first) {
   mb_grid_wait();
   mb_grid_launch_next();
   constexpr int CH = HD / 32, DB = HD / 64;
@@ -646,11 +662,16 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
   const int cta_first = past + blockIdx.x * 64;
   const int cta_last = past + min((int)blockIdx.x * 64 + 63, n_new - 1);
   const int cta_lo = (window > 0 && cta_first + 1 > window) ? cta_first + 1 - window : 0;
-  const int page0 = cta_lo / MB_PAGE, n_pages = cta_last / MB_PAGE - page0 + 1;
+  // the pages of the first keep_first positions that the window has left behind come first
+  // (kp of them, from page 0), then the window's
+  const int page0 = cta_lo / MB_PAGE;
+  const int kp = min((min(keep_first, cta_lo) + MB_PAGE - 1) / MB_PAGE, page0);
+  const int n_pages = kp + cta_last / MB_PAGE - page0 + 1;
+  auto page_at = [&](int i) { return i < kp ? i : page0 + i - kp; };
 
   auto issue = [&](int i) {  // page i of the CTA into stage i % PRE_STAGES
     if (i < n_pages) {
-      const int p = page0 + i;
+      const int p = page_at(i);
       const int entry = ring_pages > 0 ? p % ring_pages : p;
       int page = MB_INDEX_OK(entry < max_pages, 1, slot, p, max_pages)
                      ? page_table[(size_t)slot * max_pages + entry] : 0;
@@ -685,6 +706,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     const bf16* qrow = q + (size_t)(start + ra) * q_stride + (size_t)h * HD;
     load_q<HD>(has_a ? qrow : nullptr, has_b ? qrow + (size_t)8 * q_stride : nullptr, c, qa, qb);
   }
+  const float sl = slopes ? slopes[h] * 1.4426950408889634f : 0.f;   // the distance bias
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   if (sink != nullptr) {
     // one more term exp(sink[h]) in every row's denominator: a key of that score whose value
@@ -705,9 +727,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     cp_async_wait<PRE_STAGES - 2>();  // page i has landed (for this thread's copies)
     __syncthreads();                  // ... for everyone's; and page i - 1 has been read by all
     issue(i + PRE_STAGES - 1);        // into the stage that page i - 1 occupied
-    const int p = page0 + i;
-    // the pages before this warp's window and after its last row are not its business
-    if (live && p >= lo_w / MB_PAGE && p <= last_pos / MB_PAGE) {
+    const int p = page_at(i);
+    // the pages before this warp's window (unless they hold kept positions) and after its
+    // last row are not its business
+    if (live && (p >= lo_w / MB_PAGE || p * MB_PAGE < keep_first) && p <= last_pos / MB_PAGE) {
       const uint32_t ks = tiles + (i % PRE_STAGES) * STAGE, vs = ks + MB_PAGE * KP;
       const int key0 = p * MB_PAGE;
       float sc[8][4];
@@ -718,10 +741,14 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + u * 8 + 2 * c + e;
-          sc[u][e] = (key >= la && key <= pa) ? score_log2<CAP>(sc[u][e], scale_log2, cap_log2)
-                                              : -INFINITY;
-          sc[u][2 + e] = (key >= lb && key <= pb)
-                             ? score_log2<CAP>(sc[u][2 + e], scale_log2, cap_log2) : -INFINITY;
+          const bool kept = key < keep_first;
+          sc[u][e] = (key <= pa && (key >= la || kept))
+                         ? score_log2<CAP>(sc[u][e], scale_log2, cap_log2) - sl * (float)(pa - key)
+                         : -INFINITY;
+          sc[u][2 + e] = (key <= pb && (key >= lb || kept))
+                             ? score_log2<CAP>(sc[u][2 + e], scale_log2, cap_log2) -
+                                   sl * (float)(pb - key)
+                             : -INFINITY;
           mx0 = fmaxf(mx0, sc[u][e]);
           mx1 = fmaxf(mx1, sc[u][2 + e]);
         }
@@ -802,7 +829,8 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
                                    const int* seq_past, const int* seq_slot, int B, int max_new,
                                    int nh, int nkv, int hd, int window, float scale, int* error,
                                    const float* sink, float softcap, const void* gate,
-                                   int gate_stride, void* stream) {
+                                   int gate_stride, const float* slopes, int keep_first,
+                                   void* stream) {
   if (B <= 0 || max_new <= 0) return 0;
   if (hd != 64 && hd != 128)
     MB_FAIL("mb_attention_prefill: heads of %d values are not supported (64 or 128)", hd);
@@ -830,7 +858,7 @@ MB_EXPORT int mb_attention_prefill(const void* q, int q_stride, void* out, int o
               (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kpool,            \
               (const bf16*)vpool, page_table, max_pages, ring_pages, seq_start, seq_past,      \
               seq_slot, nh, nkv, window, scale_log2, sink, cap_log2, (const bf16*)gate,        \
-              gate_stride);                                                                    \
+              gate_stride, slopes, keep_first);                                                \
   }
   if (softcap > 0.f) {
     if (hd == 64) GO(64, true) else GO(128, true)
@@ -886,5 +914,5 @@ MB_EXPORT int mb_attention_decode_static(const void* q, int q_stride, void* out,
                              ring_pages, tok_slot, tok_pos, T, nh, nkv, hd, window,
                              scale, splits, g_static_scratch_ptr[device],
                              MB_ATTENTION_DECODE_STATIC_FLOATS, error, nullptr, 0.f, nullptr, 0,
-                             stream);
+                             nullptr, 0, stream);
 }

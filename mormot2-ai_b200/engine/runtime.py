@@ -166,10 +166,10 @@ class Runtime:
         c tanh(s / c) on the scaled scores; ``gate``: one logit per (token, head) whose sigmoid
         multiplies the head's output; ``slopes``: float32 [nh], taken off the scores times the
         distance; ``keep_first``: positions at a sequence's start that a window never loses."""
-        if self.fast_kernels and (not vd or vd == hd) and slopes is None and not keep_first:
+        if self.fast_kernels and (not vd or vd == hd):
             from ..parts import attention_fast
             if attention_fast.run(self, q, q_stride, out, step, line, nh, nkv, hd, window, scale,
-                                  sink, softcap, gate, gate_stride):
+                                  sink, softcap, gate, gate_stride, slopes, keep_first):
                 return
         K.attention_simt(q, q_stride, out, step, line, nh, nkv, hd, window, scale, vd, sink,
                          softcap, gate, gate_stride, slopes, keep_first)

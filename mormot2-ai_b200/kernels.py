@@ -1022,10 +1022,11 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, li
                      window: int, scale: float, splits: int, scratch: torch.Tensor,
                      error: Optional[torch.Tensor] = None,
                      sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                     gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
+                     gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
+                     slopes: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """Attention of single tokens (a decode step) over the paged cache on the tensor cores; the
-    pages of a sequence are dealt out over ``splits`` CTAs. ``softcap`` and ``gate`` as for
-    ``attention_simt``."""
+    pages of a sequence are dealt out over ``splits`` CTAs. ``softcap``, ``gate``, ``slopes``
+    and ``keep_first`` as for ``attention_simt``."""
     T = out.shape[0]
     _contig(out, "out")
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -1033,19 +1034,21 @@ def attention_decode(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, li
     assert gate is None or gate.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_decode",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-           _vp, _ll, _vp, _vp, _f, _vp, _i, _vp],
+           _vp, _ll, _vp, _vp, _f, _vp, _i, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
           _ptr(step.tok_pos), T, nh, nkv, hd, window, float(scale),
           splits, _ptr(scratch), scratch.numel(), _ptr(error), _ptr(sink), float(softcap),
-          _ptr(gate), gate_stride, _stream(), launches=2)
+          _ptr(gate), gate_stride, _ptr(slopes), int(keep_first), _stream(), launches=2)
 
 
 def attention_decode_clusters(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh,
                               nkv, hd, window: int, scale: float, splits: int,
                               error: Optional[torch.Tensor] = None,
                               sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                              gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
+                              gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
+                              slopes: Optional[torch.Tensor] = None,
+                              keep_first: int = 0) -> None:
     """``attention_decode`` with the splits of a (token, group of heads) as one thread-block
     cluster that merges through its shared memory: no scratch, one kernel; at most 8 splits."""
     T = out.shape[0]
@@ -1054,18 +1057,20 @@ def attention_decode_clusters(q: torch.Tensor, q_stride: int, out: torch.Tensor,
     assert gate is None or gate.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_decode_clusters",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _f, _i,
-           _vp, _vp, _f, _vp, _i, _vp],
+           _vp, _vp, _f, _vp, _i, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.tok_slot),
           _ptr(step.tok_pos), T, nh, nkv, hd, window, float(scale), splits, _ptr(error),
-          _ptr(sink), float(softcap), _ptr(gate), gate_stride, _stream())
+          _ptr(sink), float(softcap), _ptr(gate), gate_stride, _ptr(slopes), int(keep_first),
+          _stream())
 
 
 def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
                       hd, window: int, scale: float,
                       error: Optional[torch.Tensor] = None,
                       sink: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                      gate: Optional[torch.Tensor] = None, gate_stride: int = 0) -> None:
+                      gate: Optional[torch.Tensor] = None, gate_stride: int = 0,
+                      slopes: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """Causal attention of every sequence's new tokens over the paged cache on the tensor
     cores (the cache already holds their keys and values)."""
     _contig(out, "out")
@@ -1073,12 +1078,12 @@ def attention_prefill(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, l
     assert gate is None or gate.dtype == torch.bfloat16
     _call("attention_mma", "mb_attention_prefill",
           [_vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f,
-           _vp, _vp, _f, _vp, _i, _vp],
+           _vp, _vp, _f, _vp, _i, _vp, _i, _vp],
           _ptr(q), q_stride, _ptr(out), out.stride(0), _ptr(line.k), _ptr(line.v),
           _ptr(line.page_table), line.max_pages, line.ring_pages, _ptr(step.seq_start),
           _ptr(step.seq_past), _ptr(step.seq_slot), step.B, step.max_new, nh, nkv, hd, window,
           float(scale), _ptr(error), _ptr(sink), float(softcap), _ptr(gate), gate_stride,
-          _stream())
+          _ptr(slopes), int(keep_first), _stream())
 
 
 def attention_prefill_tc(q: torch.Tensor, q_stride: int, out: torch.Tensor, step, line, nh, nkv,
