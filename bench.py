@@ -1,7 +1,7 @@
 """Measures decoding and prefill of the Qwen3-8B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design busavik|fimudra|sezopel [--sizes small,mid]   (another workload, see below)
+    python bench.py --design busavik|fimudra|sezopel|laralix [--sizes small,mid]   (another workload, see below)
 
 A step is one decode step of a batch of 8 sequences whose context reaches 4,096 at the end of
 the timed steps. ``value`` is decoded tokens a second with the steps running back to back on
@@ -25,7 +25,10 @@ each class must compute or read. ``--design fimudra`` does the same for the Fimu
 (residual streams, attention with a sink beside a gated matrix memory, a decaying matrix
 state, routed experts with identity experts), ``--design sezopel`` for the Sezopel design
 (attention with capped scores, unit-norm heads and head gates, a layer that reads another's
-keys and values, retention, normed sublayer outputs, an input from the token after every layer).
+keys and values, retention, normed sublayer outputs, an input from the token after every layer),
+``--design laralix`` for the Laralix design (windowed attention with a distance bias beside the
+gated delta rule, attention whose values are its keys beside gated linear attention, latent
+attention with neighbours turned).
 """
 import argparse
 import json
@@ -446,6 +449,104 @@ def sezopel_shapes(name):
     return SezopelConfig.from_dict(doc), twin
 
 
+def laralix_shapes(name):
+    """A Laralix configuration whose layers have the sizes of a real model's (a ``parallel``
+    layer, a ``latent_attention`` layer and a ``parallel_2`` layer, windows of 1,024 positions
+    of which the last keeps the first 64; gated feed-forwards) and the Qwen3 configuration of
+    equal width, head count, KV heads, head size, feed-forward size, layer count and windows,
+    the closest model of this library."""
+    from mormot2_ai_b200 import LaralixConfig, Qwen3Config
+    sizes = {
+        # width, heads, kv heads, dim, state heads, state q/k heads, state dim, state vdim,
+        # latent (dim, rot_dim, vdim, kv_rank, q_rank), ff
+        "small": (1024, 8, 2, 64, 8, 4, 64, 128, (64, 32, 64, 256, 512), 2816),
+        "mid": (2048, 16, 4, 128, 16, 8, 128, 128, (128, 64, 128, 512, 768), 5632),
+    }[name]
+    w, h, kv, dim, sh, skv, sd, sv, (ld, lr, lv, kvr, qr), ff = sizes
+    vocab, window = 32768, 1024
+    mlp = {"kind": "dense", "ff": ff}
+    par = {"left": {"heads": h, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                    "softcap": 50.0, "mask": {"size": window}},
+           "right": {"heads": sh, "kv_heads": skv, "dim": sd, "vdim": sv, "conv": 4}}
+    par2 = {"left": {"heads": h, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "mask": {"size": window, "keep_first": 64}},
+            "right": {"heads": sh, "dim": sd, "vdim": sv, "tau": 16.0, "rank": 32},
+            "left_scale": 0.7, "right_scale": 0.7}
+    lat = {"heads": h, "dim": ld, "rot_dim": lr, "vdim": lv, "kv_rank": kvr, "q_rank": qr,
+           "scale": (ld + lr) ** -0.5, "rot": {"base": 1e6, "dims": lr}}
+    doc = {"architecture": "Laralix", "vocab": vocab, "width": w, "norm": {"eps": 1e-6},
+           "embedding": {"scale": w ** 0.5}, "logit_scale": 0.5,
+           "loop": {"start": 0, "stop": 3, "times": 1},
+           "layers": [{"type": "parallel", "mixer": par, "mlp": mlp},
+                      {"type": "latent_attention", "mixer": lat, "mlp": mlp},
+                      {"type": "parallel_2", "mixer": par2, "mlp": mlp}]}
+    twin = Qwen3Config(vocab_size=vocab, hidden_size=w, num_hidden_layers=3,
+                       num_attention_heads=h, num_key_value_heads=kv, head_dim=dim,
+                       intermediate_size=ff, max_position_embeddings=40960,
+                       rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+                       layer_windows=(window, 0, window))
+    return LaralixConfig.from_dict(doc), twin
+
+
+def windowed_pairs(tokens, window, keep=0):
+    """How many (query, key) pairs a prompt of ``tokens`` tokens has under a window that also
+    keeps the first ``keep`` positions (0: all earlier positions are seen)."""
+    if not window or window >= tokens:
+        return tokens * (tokens + 1) / 2
+    near = window * (window + 1) / 2 + (tokens - window) * window
+    far = sum(min(keep, i + 1 - window) for i in range(window, tokens)) if keep else 0
+    return near + far
+
+
+def laralix_work(cfg, tokens, batch, held):
+    """As ``busavik_work`` for the Laralix family: attention counts both products over the
+    pairs that the windows leave (a decode step the keys and values inside them), latent
+    attention what its kernel does, the recurrences the multiply-adds on the state (three a
+    value for the delta rule, two for gated linear attention; a decode step the state read and
+    written), the products every matrix."""
+    out = {"prefill_flops": {"attention": 0.0, "products": 0.0, "recurrence": 0.0},
+           "decode_bytes": {"attention": 0.0, "products": 0.0, "recurrence": 0.0}}
+    w = cfg.width
+    each = held / batch
+    for layer in cfg.layers:
+        m, mlp = layer["mixer"], layer.get("mlp")
+        if layer["type"] == "latent_attention":
+            h, dim, rd, vd, kvr, qr = (m[k] for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"))
+            dense = (qr + kvr + rd) * w + h * (dim + rd) * qr + h * vd * w
+            dense += h * dim * kvr + h * vd * kvr
+            out["prefill_flops"]["attention"] += 2 * h * (kvr + rd + kvr) * windowed_pairs(tokens, 0)
+            out["decode_bytes"]["attention"] += 2 * held * (kvr + rd)
+        else:
+            left, right = m["left"], m["right"]
+            h, kv, dim = left["heads"], left.get("kv_heads") or left["heads"], left["dim"]
+            vd = left.get("vdim") or dim
+            mask = left.get("mask") or {}
+            size, keep = mask.get("size") or 0, mask.get("keep_first") or 0
+            own_v = layer["type"] == "parallel"
+            dense = (h * dim + kv * dim + (kv * vd if own_v else 0) + h * vd) * w
+            out["prefill_flops"]["attention"] += 2 * h * (dim + vd) * windowed_pairs(tokens, size, keep)
+            seen = min(each, size + keep) if size else each
+            out["decode_bytes"]["attention"] += 2 * batch * seen * kv * (dim + vd)
+            sh, sd = right["heads"], right["dim"]
+            sv = right.get("vdim") or sd
+            if own_v:       # the delta rule: q and k in groups, two scalars a head, the gate
+                skv = right.get("kv_heads") or sh
+                dense += (2 * skv * sd + 2 * sh * sv + 2 * sh) * w + sh * sv * w
+                out["prefill_flops"]["recurrence"] += tokens * 6 * sh * sd * sv
+            else:           # gated linear attention: the decay's two low-rank products
+                rank = right.get("rank") or 16
+                dense += (2 * sh * sd + 2 * sh * sv + rank) * w + sh * sd * rank + sh * sv * w
+                out["prefill_flops"]["recurrence"] += tokens * 4 * sh * sd * sv
+            out["decode_bytes"]["recurrence"] += batch * 2 * 4 * sh * sd * sv
+        if mlp:
+            dense += 3 * w * mlp["ff"]
+        out["prefill_flops"]["products"] += 2 * tokens * dense
+        out["decode_bytes"]["products"] += 2 * dense
+    out["prefill_flops"]["products"] += 2 * cfg.vocab * w
+    out["decode_bytes"]["products"] += 2 * cfg.vocab * w
+    return out
+
+
 def sezopel_work(cfg, tokens, batch, held):
     """As ``busavik_work`` for the Sezopel family: attention counts both products over the
     causal pairs (a decode step the keys and values it reads, once per layer that reads them),
@@ -538,6 +639,8 @@ def busavik_work(cfg, tokens, batch, held, experts_read=None):
         return fimudra_work(cfg, tokens, batch, held, experts_read)
     if hasattr(cfg, "side_dim"):
         return sezopel_work(cfg, tokens, batch, held)
+    if getattr(cfg, "ARCHITECTURE", "") == "Laralix":
+        return laralix_work(cfg, tokens, batch, held)
     pairs = tokens * (tokens + 1) / 2
     out = {"prefill_flops": {"attention": 0.0, "products": 0.0},
            "decode_bytes": {"attention": 0.0, "products": 0.0}}
@@ -568,9 +671,14 @@ def busavik_work(cfg, tokens, batch, held, experts_read=None):
         per_layer = (cfg.q_width + 2 * cfg.kv_width) * h + h * cfg.q_width + 3 * h * i
         n = cfg.num_hidden_layers
         out["prefill_flops"]["products"] = n * 2 * tokens * per_layer + 2 * cfg.vocab_size * h
-        out["prefill_flops"]["attention"] = n * 4 * cfg.q_width * pairs
         out["decode_bytes"]["products"] = 2 * (n * per_layer + cfg.vocab_size * h)
-        out["decode_bytes"]["attention"] = n * 2 * held * 2 * cfg.kv_width
+        # a layer with a window scores and reads what the window leaves
+        windows = list(getattr(cfg, "layer_windows", None) or [0] * n)
+        out["prefill_flops"]["attention"] = sum(4 * cfg.q_width * windowed_pairs(tokens, wd)
+                                                for wd in windows)
+        out["decode_bytes"]["attention"] = sum(
+            2 * 2 * cfg.kv_width * (batch * min(held / batch, wd) if wd else held)
+            for wd in windows)
     return out
 
 
@@ -587,7 +695,8 @@ def busavik_bench(a):
     steps, warm = min(a.steps, 64), max(a.warmup, 3)
     points = {}
     for size in [v for v in a.sizes.split(",") if v]:
-        shapes = {"fimudra": fimudra_shapes, "sezopel": sezopel_shapes}.get(a.design, busavik_shapes)
+        shapes = {"fimudra": fimudra_shapes, "sezopel": sezopel_shapes,
+                  "laralix": laralix_shapes}.get(a.design, busavik_shapes)
         for family, cfg in zip((a.design, "qwen3"), shapes(size)):
             eng = Engine.from_random(cfg, seed=5, std=0.02, max_tokens=batch * ctx + tokens,
                                      max_context=max(ctx, tokens), max_slots=batch,
@@ -666,8 +775,8 @@ def main():
                     help="token counts of the long prefill points (one sequence each)")
     ap.add_argument("--only-prefill", type=int, nargs="?", const=PREFILL_TOKENS, default=0,
                     help="only a prefill of this many tokens (for profiles; prints a short line)")
-    ap.add_argument("--design", default="", choices=["", "busavik", "fimudra", "sezopel"],
-                    help="busavik, fimudra, sezopel: instead of the default workload, prefill and decode "
+    ap.add_argument("--design", default="", choices=["", "busavik", "fimudra", "sezopel", "laralix"],
+                    help="busavik, fimudra, sezopel, laralix: instead of the default workload, prefill and decode "
                          "of that design at layer sizes of real models beside the Qwen3 model of "
                          "equal size (prints its own JSON line)")
     ap.add_argument("--sizes", default="small,mid", help="with --design: which layer sizes")

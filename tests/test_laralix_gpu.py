@@ -629,6 +629,16 @@ def test_greedy_generation_through_the_entry_point(small, dtype):
     prompts = [small.tokens(n, seed=800 + n) for n in (4, 70, 17, 1)]
     steps = small.decode_steps
     got = client.generate(prompts, max_tokens=steps, temperature=0.0, stop=[])
+    # how far this engine's 16-bit logits lie from the plain ones on a prompt of this model
+    # (the other tests bound that distance): two logits that lie closer than twice that may
+    # change places
+    noise = 0.0
+    if dtype == "bfloat16":
+        probe = small.tokens(96, seed=77)
+        slot = client.engine.open()
+        out = client.engine.step([Entry(slot, probe, list(range(96)))]).cpu().numpy()
+        client.engine.close(slot)
+        noise = float(np.abs(out - small.reference(probe)).max())
     for p, tokens in zip(prompts, got):
         assert len(tokens) == steps
         ids = list(p)
@@ -636,16 +646,10 @@ def test_greedy_generation_through_the_entry_point(small, dtype):
             logits = small.reference(ids)[-1]
             order = np.argsort(-logits, kind="stable")
             if a != int(order[0]):
-                # a 16-bit run may leave the plain choice at a near tie only: where the two
-                # best logits lie closer than rounding alone moves logits of this sequence
-                # (three times the most that the plain implementation shows at any of its
-                # positions when it rounds as a 16-bit run does; measured, the engine's own
-                # differences are of that size), or than 0.06 of their spread
+                # a 16-bit run may leave the plain choice at a near tie only
                 margin = float(logits[order[0]] - logits[order[1]])
-                moved = (np.abs(small.rounded(ids, dtype) - small.reference(ids)).max()
-                         if dtype == "bfloat16" else 0.0)
-                assert dtype == "bfloat16" and margin < max(0.06 * logits.std(), 3.0 * moved), \
-                    (i, a, margin, moved)
+                assert dtype == "bfloat16" and margin < max(0.06 * logits.std(), 2.0 * noise), \
+                    (i, a, margin, noise)
                 break
             ids.append(a)
     assert all(client.engine.book.held_pages(g) == 0 for g in range(len(client.engine.plans)))
