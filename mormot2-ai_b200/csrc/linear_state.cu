@@ -11,11 +11,11 @@
 // read when a step begins and written when it ends. Everything here is float32.
 //
 // A column of the state is independent of every other column in both recurrences, so a thread
-// owns rows of ONE column in registers: P neighbouring lanes share a column's D rows (row
-// p + P r for r < R), their partial dot products meet by shuffles, and nothing else is
-// exchanged between threads inside a token. A block has a slice of a head's columns; sixteen
-// tokens are staged in shared memory at a time (q, k and the decays prepared by a warp a
-// token), then walked without a barrier.
+// owns rows of ONE column in registers: P neighbouring lanes share a column's D rows (eight
+// each), their partial dot products meet by shuffles, and nothing else is
+// exchanged between threads inside a token. A block has a slice of a head's columns; up to 32
+// tokens are staged in shared memory at a time, the next chunk's copies under way while one
+// is walked, and a chunk is walked without a barrier.
 //
 //   short_conv   y_t = silu(sum_j w[c, j] x_(t - taps + 1 + j)) per channel, the inputs before
 //                a step's first token from the state (zeros at a sequence's start)
@@ -23,7 +23,6 @@
 
 MB_DEFINE_LAST_ERROR
 
-#define LS_CT 16
 
 __device__ __forceinline__ float ls_log_sigmoid(float x) {
   return fminf(x, 0.f) - log1pf(expf(-fabsf(x)));
@@ -129,21 +128,35 @@ struct LsArgs {
   const int* seq_slot;
   void* out;             // [T, H * DV] of the activation type (one slice of columns a head)
   float* raw;            // [T, H * DV] float32 (several slices; normed by a kernel after)
-  int H, D, DV, P, CW;
+  int H, D, DV, P, CW, CT;
 };
 
+__device__ __forceinline__ void ls_copy4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ls_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ls_wait_but_one() {
+  asm volatile("cp.async.wait_group 1;" ::: "memory");
+}
+
+// Shared memory: two buffers, each [q | k | decay logits (mode 0)] of CT tokens x DP values and
+// CT x CW values of v; then CT x CW outputs and four numbers a token. A token's D values of
+// q, k and the decays lie in P parts of R + 4 places (R used): part p is what lane p of a
+// column reads, sixteen bytes at a time, and the four places of padding keep the parts of a
+// warp on different banks. While a chunk is walked the next one's values are already on their
+// way (asynchronous copies of four bytes, whatever the alignment of the rows).
 template <typename T, int MODE, int R>
 __global__ void __launch_bounds__(512, 1) linear_state_scan_kernel(const LsArgs a) {
   mb_grid_wait();
   mb_grid_launch_next();
   extern __shared__ __align__(16) float ls_smem[];
-  const int D = a.D, DV = a.DV, P = a.P, CW = a.CW, Dp = P * R;
-  float* sq = ls_smem;                        // [CT][Dp], zeros behind D
-  float* sk = sq + LS_CT * Dp;                // [CT][Dp]
-  float* sa = sk + LS_CT * Dp;                // [CT][Dp] (mode 0)
-  float* sv = sa + (MODE == 0 ? LS_CT * Dp : 0);   // [CT][CW]
-  float* so = sv + LS_CT * CW;                // [CT][CW]
-  float* sc = so + LS_CT * CW;                // [CT][2]: decay, beta (mode 1)
+  constexpr int RP = R + 4, NV = MODE == 0 ? 3 : 2;
+  const int D = a.D, DV = a.DV, P = a.P, CW = a.CW, CT = a.CT, DP = P * RP;
+  const int BUF = NV * CT * DP + CT * CW;
+  float* so = ls_smem + 2 * BUF;              // [CT][CW]
+  float* sc = so + CT * CW;                   // [2][CT][8]: decay, beta, factor of q, factor of k,
+                                              // k . q; places 6 and 7 receive the two logits
   const int b = blockIdx.x, hd = blockIdx.y, g = hd / a.group;
   const int c0 = blockIdx.z * CW, cw = max(0, min(DV, c0 + CW) - c0);
   const int j = threadIdx.x / P, p = threadIdx.x - j * P;
@@ -152,98 +165,162 @@ __global__ void __launch_bounds__(512, 1) linear_state_scan_kernel(const LsArgs 
   float* Sg = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.state_off +
               (size_t)hd * D * DV + c0;
   const bool own = j < cw;
+  // the places that no copy writes (padding, rows behind D, columns behind cw) stay zero
+  for (int e = threadIdx.x; e < 2 * BUF; e += blockDim.x) ls_smem[e] = 0.f;
   float S[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = p + P * r;
+    const int i = p * R + r;
     S[r] = (own && i < D) ? Sg[(size_t)i * DV + j] : 0.f;
   }
+  __syncthreads();
   const float q_scale = rsqrtf((float)D);
-  for (int c = 0; c < n; c += LS_CT) {
-    const int cn = min(LS_CT, n - c);
-    // a warp a token: q and k (and the decays) as the recurrence takes them
-    for (int tt = warp; tt < cn; tt += warps) {
-      const size_t row = (size_t)(t0 + c + tt);
-      const float* qr = a.qkv + row * a.ldq + a.cq + g * D;
-      const float* kr = a.qkv + row * a.ldq + a.ck + g * D;
-      float fq = q_scale, fk = 1.f;
-      if (MODE == 1) {
-        float ssq = 0.f, ssk = 0.f;
+  const int chunks = (n + CT - 1) / CT;
+
+  auto issue = [&](int ci) {      // chunk ci into buffer ci & 1
+    if (ci < chunks) {
+      float* qb = ls_smem + (ci & 1) * BUF;
+      float* kb = qb + CT * DP;
+      float* ab = kb + CT * DP;
+      float* vb = qb + NV * CT * DP;
+      const int cn = min(CT, n - ci * CT);
+      for (int tt = warp; tt < cn; tt += warps) {       // a warp a token, a value a lane
+        const size_t row = (size_t)(t0 + ci * CT + tt);
+        const float* qr = a.qkv + row * a.ldq + a.cq + g * D;
+        const float* kr = a.qkv + row * a.ldq + a.ck + g * D;
+        const float* ar = MODE == 0 ? a.za + row * a.lda + a.ca + hd * D : nullptr;
         for (int i = lane; i < D; i += 32) {
-          ssq = fmaf(qr[i], qr[i], ssq);
-          ssk = fmaf(kr[i], kr[i], ssk);
+          const int dst = tt * DP + (i / R) * RP + (i % R);
+          ls_copy4(qb + dst, qr + i);
+          ls_copy4(kb + dst, kr + i);
+          if (MODE == 0) ls_copy4(ab + dst, ar + i);
         }
-        fq = q_scale / sqrtf(warp_sum(ssq) + a.unit_eps);
-        fk = 1.0f / sqrtf(warp_sum(ssk) + a.unit_eps);
-        if (lane == 0) {
-          const float zb = a.zs[row * a.lds + a.cb + hd], zd = a.zs[row * a.lds + a.cd + hd];
-          sc[2 * tt] = expf(-expf(a.a_log[hd]) * ls_softplus(zd + a.dt_bias[hd]));
-          sc[2 * tt + 1] = 1.0f / (1.0f + expf(-zb));
-        }
-      }
-      for (int i = lane; i < Dp; i += 32) {
-        sq[tt * Dp + i] = i < D ? qr[i] * fq : 0.f;
-        sk[tt * Dp + i] = i < D ? kr[i] * fk : 0.f;
-        if (MODE == 0)
-          sa[tt * Dp + i] = i < D ? expf(ls_log_sigmoid(a.za[row * a.lda + a.ca + hd * D + i] +
-                                                        a.abias[hd * D + i]) * a.inv_tau)
-                                  : 0.f;
+        const float* vr = a.qkv + row * a.ldq + a.cv + hd * DV + c0;
+        for (int jj = lane; jj < cw; jj += 32) ls_copy4(vb + tt * CW + jj, vr + jj);
+        if (MODE == 1 && lane < 2)
+          ls_copy4(sc + ((ci & 1) * CT + tt) * 8 + 6 + lane,
+                   a.zs + row * a.lds + (lane ? a.cd : a.cb) + hd);
       }
     }
-    for (int e = threadIdx.x; e < cn * CW; e += blockDim.x) {
-      const int tt = e / CW, jj = e - tt * CW;
-      sv[e] = jj < cw ? a.qkv[(size_t)(t0 + c + tt) * a.ldq + a.cv + hd * DV + c0 + jj] : 0.f;
+    ls_commit();
+  };
+
+  issue(0);
+  for (int ci = 0; ci < chunks; ++ci) {
+    const int cn = min(CT, n - ci * CT);
+    issue(ci + 1);
+    ls_wait_but_one();            // chunk ci has landed (this thread's copies)
+    __syncthreads();              // ... everyone's
+    float* qb = ls_smem + (ci & 1) * BUF;
+    float* kb = qb + CT * DP;
+    float* ab = kb + CT * DP;
+    const float* vb = qb + NV * CT * DP;
+    if (MODE == 0) {
+      // the decays: sigmoid(z + bias)^(1 / tau), in place
+      for (int tt = warp; tt < cn; tt += warps)
+        for (int i = lane; i < D; i += 32) {
+          const int at = tt * DP + (i / R) * RP + (i % R);
+          ab[at] = expf(ls_log_sigmoid(ab[at] + a.abias[hd * D + i]) * a.inv_tau);
+        }
+    } else {
+      // a warp a token: the factors that bring q and k to unit length, the decay and beta
+      for (int tt = warp; tt < cn; tt += warps) {
+        float ssq = 0.f, ssk = 0.f, dot = 0.f;
+        for (int i = lane; i < D; i += 32) {
+          const int at = tt * DP + (i / R) * RP + (i % R);
+          ssq = fmaf(qb[at], qb[at], ssq);
+          ssk = fmaf(kb[at], kb[at], ssk);
+          dot = fmaf(kb[at], qb[at], dot);
+        }
+        ssq = warp_sum(ssq);
+        ssk = warp_sum(ssk);
+        dot = warp_sum(dot);
+        if (lane == 0) {
+          float* n8 = sc + ((ci & 1) * CT + tt) * 8;
+          const float zb = n8[6], zd = n8[7];
+          n8[0] = expf(-expf(a.a_log[hd]) * ls_softplus(zd + a.dt_bias[hd]));
+          n8[1] = 1.0f / (1.0f + expf(-zb));
+          n8[2] = q_scale / sqrtf(ssq + a.unit_eps);
+          n8[3] = 1.0f / sqrtf(ssk + a.unit_eps);
+          n8[4] = dot;
+        }
+      }
     }
     __syncthreads();
     for (int tt = 0; tt < cn; ++tt) {
-      const float vj = sv[tt * CW + min(j, CW - 1)];
-      const float* q = sq + tt * Dp + p;
-      const float* k = sk + tt * Dp + p;
-      float o0 = 0.f, o1 = 0.f;
+      const float vj = vb[tt * CW + min(j, CW - 1)];
+      const float4* q4 = (const float4*)(qb + tt * DP + p * RP);
+      const float4* k4 = (const float4*)(kb + tt * DP + p * RP);
+      float o0 = 0.f, o1 = 0.f, o;
       if (MODE == 0) {
-        const float* al = sa + tt * Dp + p;
+        const float4* a4 = (const float4*)(ab + tt * DP + p * RP);
 #pragma unroll
-        for (int r = 0; r < R; r += 2) {
-          S[r] = fmaf(al[P * r], S[r], k[P * r] * vj);
-          o0 = fmaf(S[r], q[P * r], o0);
-          S[r + 1] = fmaf(al[P * (r + 1)], S[r + 1], k[P * (r + 1)] * vj);
-          o1 = fmaf(S[r + 1], q[P * (r + 1)], o1);
+        for (int r = 0; r < R; r += 4) {
+          const float4 al = a4[r >> 2], kk = k4[r >> 2], qq = q4[r >> 2];
+          S[r] = fmaf(al.x, S[r], kk.x * vj);
+          S[r + 1] = fmaf(al.y, S[r + 1], kk.y * vj);
+          S[r + 2] = fmaf(al.z, S[r + 2], kk.z * vj);
+          S[r + 3] = fmaf(al.w, S[r + 3], kk.w * vj);
+          o0 = fmaf(S[r], qq.x, o0);
+          o1 = fmaf(S[r + 1], qq.y, o1);
+          o0 = fmaf(S[r + 2], qq.z, o0);
+          o1 = fmaf(S[r + 3], qq.w, o1);
         }
+        o = (o0 + o1) * q_scale;
       } else {
-        const float dec = sc[2 * tt], beta = sc[2 * tt + 1];
+        // With S' = g S: the read-out (S' + k u^T)^T q = S'^T q + u (k . q), so the sums over the
+        // rows of S'^T k and of S'^T q are formed side by side and meet in one round of
+        // shuffles; the write into the state is off the path to the output.
+        const float* n8 = sc + ((ci & 1) * CT + tt) * 8;
+        const float dec = n8[0], beta = n8[1], fq = n8[2], fk = n8[3], kq = n8[4];
         float p0 = 0.f, p1 = 0.f;
+        float4 kk[R / 4];
 #pragma unroll
-        for (int r = 0; r < R; r += 2) {
+        for (int r = 0; r < R; r += 4) {
+          kk[r >> 2] = k4[r >> 2];
+          const float4 qq = q4[r >> 2];
           S[r] *= dec;
-          p0 = fmaf(S[r], k[P * r], p0);
           S[r + 1] *= dec;
-          p1 = fmaf(S[r + 1], k[P * (r + 1)], p1);
+          S[r + 2] *= dec;
+          S[r + 3] *= dec;
+          p0 = fmaf(S[r], kk[r >> 2].x, p0);
+          p1 = fmaf(S[r + 1], kk[r >> 2].y, p1);
+          p0 = fmaf(S[r + 2], kk[r >> 2].z, p0);
+          p1 = fmaf(S[r + 3], kk[r >> 2].w, p1);
+          o0 = fmaf(S[r], qq.x, o0);
+          o1 = fmaf(S[r + 1], qq.y, o1);
+          o0 = fmaf(S[r + 2], qq.z, o0);
+          o1 = fmaf(S[r + 3], qq.w, o1);
         }
-        float pred = p0 + p1;
-        for (int m = 1; m < P; m <<= 1) pred += __shfl_xor_sync(0xffffffffu, pred, m);
-        const float u = beta * (vj - pred);
+        float pred = p0 + p1, read = o0 + o1;
+        for (int m = 1; m < P; m <<= 1) {
+          pred += __shfl_xor_sync(0xffffffffu, pred, m);
+          read += __shfl_xor_sync(0xffffffffu, read, m);
+        }
+        const float uk = beta * (vj - pred * fk) * fk;     // u times the unit key's factor
 #pragma unroll
-        for (int r = 0; r < R; r += 2) {
-          S[r] = fmaf(k[P * r], u, S[r]);
-          o0 = fmaf(S[r], q[P * r], o0);
-          S[r + 1] = fmaf(k[P * (r + 1)], u, S[r + 1]);
-          o1 = fmaf(S[r + 1], q[P * (r + 1)], o1);
+        for (int r = 0; r < R; r += 4) {
+          S[r] = fmaf(kk[r >> 2].x, uk, S[r]);
+          S[r + 1] = fmaf(kk[r >> 2].y, uk, S[r + 1]);
+          S[r + 2] = fmaf(kk[r >> 2].z, uk, S[r + 2]);
+          S[r + 3] = fmaf(kk[r >> 2].w, uk, S[r + 3]);
         }
+        o = (read + uk * kq) * fq;
       }
-      float o = o0 + o1;
-      for (int m = 1; m < P; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+      if (MODE == 0)
+        for (int m = 1; m < P; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
       if (p == 0 && own) so[tt * CW + j] = o;
     }
     __syncthreads();
     if (a.raw != nullptr) {
-      for (int e = threadIdx.x; e < cn * cw; e += blockDim.x) {
-        const int tt = e / cw, jj = e - tt * cw;
-        a.raw[(size_t)(t0 + c + tt) * a.H * DV + hd * DV + c0 + jj] = so[tt * CW + jj];
+      for (int tt = warp; tt < cn; tt += warps) {
+        float* rr = a.raw + (size_t)(t0 + ci * CT + tt) * a.H * DV + hd * DV + c0;
+        for (int jj = lane; jj < cw; jj += 32) rr[jj] = so[tt * CW + jj];
       }
     } else {
       // one slice: the head's norm, its weight and the gate here, a warp a token
       for (int tt = warp; tt < cn; tt += warps) {
-        const size_t row = (size_t)(t0 + c + tt);
+        const size_t row = (size_t)(t0 + ci * CT + tt);
         float ss = 0.f;
         for (int i = lane; i < DV; i += 32) ss = fmaf(so[tt * CW + i], so[tt * CW + i], ss);
         const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)DV + a.eps);
@@ -259,7 +336,7 @@ __global__ void __launch_bounds__(512, 1) linear_state_scan_kernel(const LsArgs 
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = p + P * r;
+    const int i = p * R + r;
     if (own && i < D) Sg[(size_t)i * DV + j] = S[r];
   }
 }
@@ -285,13 +362,14 @@ __global__ void ls_head_norm_kernel(const float* __restrict__ raw, const float* 
   }
 }
 
-// how the rows of a column are dealt: P lanes (a power of two, at most 8) with R rows each
-static void ls_shape(int D, int* P, int* R) {
+// how the rows of a column are dealt: P lanes (a power of two, at most 32) with 8 rows each.
+// Few rows a lane make many light warps: a warp's time a token is the latency of its chain of
+// multiply-adds and shuffles, and several warps a scheduler hide one another's.
+#define LS_ROWS 8
+static int ls_parts(int D) {
   int p = 1;
-  while (p < 8 && (D + p - 1) / p > 16) p *= 2;
-  const int per = (D + p - 1) / p;
-  *P = p;
-  *R = per <= 8 ? 8 : per <= 16 ? 16 : 32;
+  while (p < 32 && p * LS_ROWS < D) p *= 2;
+  return p;
 }
 
 // mode 0: gated linear attention; mode 1: gated delta rule. `raw`: float32 [T, H * DV] of
@@ -305,8 +383,8 @@ MB_EXPORT int mb_linear_state_scan(int mode, const float* qkv, int ldq, int cq, 
                                    const float* normw, float eps, float* state,
                                    long long state_stride, long long state_off,
                                    const int* seq_start, const int* seq_slot, void* out,
-                                   float* raw, int out_dtype, int T_, int B, int H, int D, int DV,
-                                   void* stream) {
+                                   float* raw, int out_dtype, int T_, int B, int max_new, int H,
+                                   int D, int DV, void* stream) {
   if (B <= 0 || T_ <= 0) return 0;
   if (D <= 0 || D > 256 || DV <= 0 || DV > 1024)
     MB_FAIL("mb_linear_state_scan: heads of %d x %d values (at most 256 x 1024)", D, DV);
@@ -318,8 +396,7 @@ MB_EXPORT int mb_linear_state_scan(int mode, const float* qkv, int ldq, int cq, 
   a.unit_eps = unit_eps; a.gate = gate; a.ldg = ldg; a.cg = cg; a.normw = normw; a.eps = eps;
   a.state = state; a.state_stride = (size_t)state_stride; a.state_off = (size_t)state_off;
   a.seq_start = seq_start; a.seq_slot = seq_slot; a.out = out; a.H = H; a.D = D; a.DV = DV;
-  int P, R;
-  ls_shape(D, &P, &R);
+  const int P = ls_parts(D), R = LS_ROWS;
   // a block's slice of the columns: all of them while the step has blocks enough (and they fit
   // a block), else slices of 32 so that a single prompt does not leave the device idle
   int CW = DV;
@@ -330,8 +407,20 @@ MB_EXPORT int mb_linear_state_scan(int mode, const float* qkv, int ldq, int cq, 
   if (NS > 1 && raw == nullptr) MB_FAIL("mb_linear_state_scan: value rows of %d need scratch", DV);
   a.P = P; a.CW = CW; a.raw = NS > 1 ? raw : nullptr;
   const int threads = (CW * P + 31) / 32 * 32;
-  const size_t smem = ((size_t)LS_CT * P * R * (mode == 0 ? 3 : 2) + 2 * LS_CT * CW + 2 * LS_CT) *
-                      sizeof(float);
+  // tokens staged at once: 32, or fewer where a sequence brings fewer (a decode step) or two
+  // buffers of them would not fit
+  int CT = 32;
+  while (CT > 4 && CT / 2 >= max_new) CT /= 2;
+  size_t smem = 0;
+  for (;; CT /= 2) {
+    const size_t buf = (size_t)(mode == 0 ? 3 : 2) * CT * P * (R + 4) + (size_t)CT * CW;
+    smem = (2 * buf + (size_t)CT * CW + 16 * CT) * sizeof(float);
+    if (smem <= 160 * 1024 || CT == 4) break;
+  }
+  if (smem > 200 * 1024)
+    MB_FAIL("mb_linear_state_scan: heads of %d x %d values need %zu bytes of shared memory", D,
+            DV, smem);
+  a.CT = CT;
   cudaStream_t s = (cudaStream_t)stream;
 #define GO(T_t, M_, R_)                                                                        \
   {                                                                                            \
@@ -346,12 +435,7 @@ MB_EXPORT int mb_linear_state_scan(int mode, const float* qkv, int ldq, int cq, 
       mb_launch(ls_head_norm_kernel<T_t>, dim3((T_ * H + 3) / 4), dim3(128), 0, s,             \
                 (const float*)raw, gate, ldg, cg, normw, eps, (T_t*)out, T_ * H, H, DV);       \
   }
-#define GOR(T_t, M_)                                                                           \
-  switch (R) {                                                                                 \
-    case 8: GO(T_t, M_, 8) break;                                                              \
-    case 16: GO(T_t, M_, 16) break;                                                            \
-    default: GO(T_t, M_, 32)                                                                   \
-  }
+#define GOR(T_t, M_) GO(T_t, M_, LS_ROWS)
 #define GOM(T_t)                                                                               \
   if (mode == 0) { GOR(T_t, 0) } else { GOR(T_t, 1) }
   if (out_dtype == MB_F32) { GOM(float) } else { GOM(__nv_bfloat16) }

@@ -654,7 +654,7 @@ def linear_state_scan(mode: str, qkv: torch.Tensor, cols, group: int, gate: torc
     raw = torch.empty((T, heads * vdim), dtype=f32, device=out.device)
     _call("linear_state", "mb_linear_state_scan",
           [_i, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _f, _vp, _i, _i, _i, _vp, _vp, _f,
-           _vp, _i, _i, _vp, _f, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+           _vp, _i, _i, _vp, _f, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
           0 if mode == "gla" else 1, _ptr(qkv), qkv.stride(0), *[int(c) for c in cols],
           int(group), _ptr(decay_logits),
           decay_logits.stride(0) if decay_logits is not None else 0, int(decay_col),
@@ -662,8 +662,8 @@ def linear_state_scan(mode: str, qkv: torch.Tensor, cols, group: int, gate: torc
           scalars.stride(0) if scalars is not None else 0, int(beta_col), int(rate_col),
           _ptr(a_log), _ptr(dt_bias), float(unit_eps), _ptr(gate), gate.stride(0), int(gate_col),
           _ptr(normw), float(eps), _ptr(state), state.stride(0), 0, _ptr(step.seq_start),
-          _ptr(step.seq_slot), _ptr(out), _ptr(raw), code_of(out.dtype), T, step.B, heads, dim,
-          vdim, _stream(), launches=2 if sliced else 1)
+          _ptr(step.seq_slot), _ptr(out), _ptr(raw), code_of(out.dtype), T, step.B, step.max_new,
+          heads, dim, vdim, _stream(), launches=2 if sliced else 1)
 
 
 # ------------------------------------------------------------------------------ latent attention
