@@ -283,10 +283,11 @@ MB_EXPORT int mb_swiglu(const void* in, void* out, int dtype, int T, int I, void
 
 // ------------------------------------------------------------------ decode without the host
 // Between two decode steps that run without a host round trip: the tokens just chosen become
-// the next step's input ids and every position moves on by one.
+// the next step's input ids and every position moves on by one (and with it what a sequence
+// held before the step, which kernels that walk sequences rather than tokens read).
 __global__ void advance_decode_kernel(int* __restrict__ tok_ids, int* __restrict__ tok_pos,
                                       const int* __restrict__ chosen, int* __restrict__ history,
-                                      int B) {
+                                      int* __restrict__ seq_past, int B) {
   mb_grid_wait();
   mb_grid_launch_next();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -294,14 +295,15 @@ __global__ void advance_decode_kernel(int* __restrict__ tok_ids, int* __restrict
   const int t = chosen[b];
   tok_ids[b] = t;
   tok_pos[b] += 1;
+  if (seq_past) seq_past[b] += 1;
   if (history) history[b] = t;
 }
 
 MB_EXPORT int mb_advance_decode(int* tok_ids, int* tok_pos, const int* chosen, int* history,
-                                int B, void* stream) {
+                                int* seq_past, int B, void* stream) {
   if (B <= 0) return 0;
   mb_launch(advance_decode_kernel, dim3((B + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tok_ids, tok_pos,
-                                                                          chosen, history, B);
+                                                                          chosen, history, seq_past, B);
   MB_CHECK_LAUNCH("mb_advance_decode");
 }
 

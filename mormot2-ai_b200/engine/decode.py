@@ -69,7 +69,8 @@ class DecodeRun:
         logits = eng._forward(ctx)
         self.sampler.pick(logits, ctx.seq_slot, self.sampling, self.vocab_limit, out=self.box)
         K.advance_decode(ctx.tok_ids, ctx.tok_pos, self.box,
-                         self.history[self.launched] if self.history is not None else None)
+                         self.history[self.launched] if self.history is not None else None,
+                         ctx.seq_past)
         if self.history is None:
             rt.post_mail(self.launched % self.DEPTH, ctx.B)
         eng.passes += 1

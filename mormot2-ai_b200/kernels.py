@@ -998,12 +998,16 @@ def wait_selftest(error: torch.Tensor, code: int, tries: int = 2048) -> bool:
 
 
 def advance_decode(tok_ids: torch.Tensor, tok_pos: torch.Tensor, chosen: torch.Tensor,
-                   history: Optional[torch.Tensor]) -> None:
-    """The chosen tokens become the next step's ids, every position moves on by one."""
+                   history: Optional[torch.Tensor],
+                   seq_past: Optional[torch.Tensor] = None) -> None:
+    """The chosen tokens become the next step's ids, every position moves on by one;
+    ``seq_past`` (what every sequence held before the step) moves on with them."""
     B = tok_ids.numel()
     assert chosen.dtype == torch.int32 and chosen.numel() == B
-    _call("elementwise", "mb_advance_decode", [_vp, _vp, _vp, _vp, _i, _vp],
-          _ptr(tok_ids), _ptr(tok_pos), _ptr(chosen), _ptr(history), B, _stream())
+    assert seq_past is None or (seq_past.dtype == torch.int32 and seq_past.numel() == B)
+    _call("elementwise", "mb_advance_decode", [_vp, _vp, _vp, _vp, _vp, _i, _vp],
+          _ptr(tok_ids), _ptr(tok_pos), _ptr(chosen), _ptr(history), _ptr(seq_past), B,
+          _stream())
 
 
 def sample_filtered(logits: torch.Tensor, sampling, state_index: torch.Tensor,

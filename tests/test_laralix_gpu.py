@@ -624,21 +624,31 @@ def test_decode_graphs_replay_what_was_computed(small_a):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_generation_runs_pick_what_single_steps_pick(small, dtype):
+    """The generation loop decodes in runs whose token ids, positions and lengths move on in
+    device memory; a sequence alone must get the very tokens that the step function gives it
+    one step at a time (the same kernels on the same numbers)."""
+    client = LlmClient(small.folder, dtype=dtype, max_batch=2, cache_tokens=1024)
+    eng = client.engine
+    for n in (1, 70):
+        p = small.tokens(n, seed=900 + n)
+        got = client.generate([p], max_tokens=8, temperature=0.0, stop=[])[0]
+        slot = eng.open()
+        logits = eng.step([Entry(slot, p)]).cpu().numpy()
+        want = []
+        for _ in range(8):
+            want.append(int(logits[-1].argmax()))
+            logits = eng.step([Entry(slot, [want[-1]])]).cpu().numpy()
+        eng.close(slot)
+        assert got == want, (n, got, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_greedy_generation_through_the_entry_point(small, dtype):
     client = LlmClient(small.folder, dtype=dtype, max_batch=3, cache_tokens=1024)
     prompts = [small.tokens(n, seed=800 + n) for n in (4, 70, 17, 1)]
     steps = small.decode_steps
     got = client.generate(prompts, max_tokens=steps, temperature=0.0, stop=[])
-    # how far this engine's 16-bit logits lie from the plain ones on a prompt of this model
-    # (the other tests bound that distance): two logits that lie closer than twice that may
-    # change places
-    noise = 0.0
-    if dtype == "bfloat16":
-        probe = small.tokens(96, seed=77)
-        slot = client.engine.open()
-        out = client.engine.step([Entry(slot, probe, list(range(96)))]).cpu().numpy()
-        client.engine.close(slot)
-        noise = float(np.abs(out - small.reference(probe)).max())
     for p, tokens in zip(prompts, got):
         assert len(tokens) == steps
         ids = list(p)
@@ -648,8 +658,7 @@ def test_greedy_generation_through_the_entry_point(small, dtype):
             if a != int(order[0]):
                 # a 16-bit run may leave the plain choice at a near tie only
                 margin = float(logits[order[0]] - logits[order[1]])
-                assert dtype == "bfloat16" and margin < max(0.06 * logits.std(), 2.0 * noise), \
-                    (i, a, margin, noise)
+                assert dtype == "bfloat16" and margin < 0.06 * logits.std(), (i, a, margin)
                 break
             ids.append(a)
     assert all(client.engine.book.held_pages(g) == 0 for g in range(len(client.engine.plans)))
