@@ -662,3 +662,52 @@ def test_greedy_generation_through_the_entry_point(small, dtype):
                 break
             ids.append(a)
     assert all(client.engine.book.held_pages(g) == 0 for g in range(len(client.engine.plans)))
+
+
+def test_steps_replayed_through_the_trace_runner(small_a, tmp_path):
+    """``bin/trace_run`` as a user runs it: requests of unequal lengths start in one step, go on
+    by one token together, the shorter ones end earlier, and other requests follow in the
+    slots, pages and states that were given back. ``--max-tokens`` counts the tokens that live
+    requests hold, no padding."""
+    import json
+    import subprocess
+    import sys
+    from tests.conftest import ROOT
+    small = small_a
+    lens, tails = [1, 70, 130, 9, 66, 3], [2, 5, 3, 4, 1, 6]
+    reqs = {f"q{i}": small.tokens(n + t, seed=950 + i) for i, (n, t) in enumerate(zip(lens, tails))}
+    steps, expect, n = [], {}, 0
+    for batch in (["q0", "q1", "q2"], ["q3", "q4", "q5"]):
+        at = {r: lens[int(r[1:])] for r in batch}
+        steps.append({"step": n, "end": [],
+                      "entries": [{"id": r, "tokens": reqs[r][:at[r]], "want": [at[r] - 1]}
+                                  for r in batch]})
+        expect[n] = [(r, at[r] - 1) for r in batch]
+        n += 1
+        live = list(batch)
+        while live:
+            entries = [{"id": r, "tokens": [reqs[r][at[r]]], "want": [0]} for r in live]
+            expect[n] = [(r, at[r]) for r in live]
+            for r in live:
+                at[r] += 1
+            ended = [r for r in live if at[r] >= len(reqs[r])]
+            steps.append({"step": n, "entries": entries, "end": ended})
+            live = [r for r in live if r not in ended]
+            n += 1
+    most = max(sum(len(reqs[r]) for r in batch) for batch in (["q0", "q1", "q2"], ["q3", "q4", "q5"]))
+    for dtype in DTYPES:
+        out = tmp_path / dtype
+        p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model",
+                            small.folder, "--dtype", dtype, "--out", str(out), "--max-tokens",
+                            str(most)], input="".join(json.dumps(s) + "\n" for s in steps),
+                           capture_output=True, text=True, timeout=900)
+        assert p.returncode == 0, p.stderr[-3000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == \
+            [f"done {s['step']}" for s in steps]
+        refs = {r: small.reference(ids) for r, ids in reqs.items()}
+        moved = {r: small.rounded(ids, dtype) for r, ids in reqs.items()}
+        for step, wanted in expect.items():
+            got = np.fromfile(str(out / f"{step}.f32"), dtype="<f4").reshape(-1, small.doc["vocab"])
+            want = np.stack([refs[r][t] for r, t in wanted])
+            check(got, want, dtype, f"step {step}",
+                  None if dtype != "bfloat16" else np.stack([moved[r][t] for r, t in wanted]))

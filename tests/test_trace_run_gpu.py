@@ -98,7 +98,8 @@ def test_unequal_batches(tiny, dtype, tmp_path):
             live = [rid for rid in live if rid not in ended]      # shorter requests end earlier
             n += 1
     most = max(sum(-(-len(reqs[rid]) // 64) * 64 for rid in batch) for batch in batches)
-    replay(tiny.folder, dtype, steps, tmp_path, max_tokens=most)  # pages must be used again
+    # pages must be used again
+    replay(tiny.folder, dtype, steps, tmp_path, max_tokens=most, more=["--no-slack"])
     refs = {rid: tiny.reference(ids) for rid, ids in reqs.items()}
     for step, wanted in expect.items():
         got = logits_of(tmp_path, step, vocab)
