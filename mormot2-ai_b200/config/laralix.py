@@ -318,4 +318,6 @@ class LaralixConfig:
             positions=positions, layers=tuple(layers), schedule=tuple(schedule),
             final_norm=norm("final.norm"),
             head=PartSpec("lm_head", {"name": "head", "tied": False, "vocab_size": c.vocab,
-                                      "hidden_size": c.width, "scale": c.logit_scale}))
+                                      "hidden_size": c.width, "scale": c.logit_scale}),
+            # a model without a loop may still store the passes' vectors: tolerated, unused
+            tolerated=() if c.loop is not None else (("loop.step", (-1, c.width)),))

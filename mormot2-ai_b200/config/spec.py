@@ -71,6 +71,9 @@ class ModelSpec:
     final_norm: PartSpec           # params: name, eps, size
     head: PartSpec                 # params: name, tied
     streams: int = 0               # > 0: the residual is that many streams [streams, T, hidden]
+    # tensors that a folder may store although this model does not use them: (name, shape with
+    # -1 for any size)
+    tolerated: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
     def cache_lines(self) -> int:
         lines = [r.cache_line for r in self.schedule if r.cache_line is not None]

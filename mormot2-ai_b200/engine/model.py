@@ -74,6 +74,8 @@ class DecoderModel:
                     raise ConfigError(f"{need.name} is bound with two shapes")
                 if need.name not in seen or not need.optional:
                     seen[need.name] = need
+        for name, shape in self.spec.tolerated:
+            seen.setdefault(name, TensorNeed(name, tuple(shape), "bias", optional=True))
         return list(seen.values())
 
     def _check_lines(self) -> None:

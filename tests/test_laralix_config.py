@@ -204,3 +204,12 @@ def test_plain_delta_rule_replaces_what_a_key_holds():
     # the second read-out sees only the second value (the first was taken back out)
     assert abs(out[1, 0]) < 1e-3 * abs(out[1, 1]) and out[1, 1] > 0
     assert out[0, 0] > 0 and abs(out[0, 1]) < 1e-9
+
+
+def test_a_model_without_a_loop_may_store_the_passes_vectors():
+    spec = LaralixConfig.from_dict(small_doc("B")).to_model_spec()
+    needs = {t.name: t for t in DecoderModel(spec).tensors()}
+    assert needs["loop.step"].optional and needs["loop.step"].shape == (-1, 40)
+    looped = {t.name: t for t in DecoderModel(
+        LaralixConfig.from_dict(small_doc("A")).to_model_spec()).tensors()}
+    assert not looped["loop.step"].optional
